@@ -6,8 +6,9 @@ from .registry import (
 from .llama import LlamaConfig
 from .ramupel import RamupelConfig
 from .botuvik import BotuvikConfig
+from .zasitar import ZasitarConfig
 
 __all__ = [
-    "ArchitectureConfig", "BotuvikConfig", "LlamaConfig", "RamupelConfig", "config_class_for", "config_from_dict",
+    "ArchitectureConfig", "BotuvikConfig", "LlamaConfig", "RamupelConfig", "ZasitarConfig", "config_class_for", "config_from_dict",
     "known_architectures", "load_config", "register_architecture", "unregister_architecture",
 ]

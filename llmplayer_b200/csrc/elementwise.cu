@@ -622,6 +622,8 @@ extern "C" int lp_advance(int* tokens, int* positions, int* kv_len, const int* s
 // size: queries, keys and values are stored with `hdp` features per head (hdp >= dk, dv), the rest zero, so that the
 // attention kernels see one head size; queries go to q_out[t, h, :hdp], keys and values to the page of the token's
 // sequence that holds its position, pages[page][0|1][g][position % page_size][:hdp]. A warp per head; all float32.
+// `qgain` / `kgain` (optional, [dk], shared by the heads): BEFORE the rotation every query / key head is RMS-normed
+// over dk with that gain and `gain_eps` inside the root. G = 0 with `pages` null: a layer that has queries only.
 constexpr int PREP_MAX = 256;
 template <typename TQ, typename TKV>
 __global__ void __launch_bounds__(256)
@@ -629,7 +631,7 @@ qkv_prepare_kernel(const float* __restrict__ qkv, int ld, const float* __restric
                    const int* __restrict__ positions, const int* __restrict__ seq_ids, const int* __restrict__ page_table,
                    int pt_stride, TQ* __restrict__ q_out, TKV* __restrict__ pages, int H, int G, int dk, int dv, int hdp,
                    int rd, int interleaved, int unit, float unit_eps, int page_size, float* __restrict__ zero,
-                   long long zero_count) {
+                   long long zero_count, const float* __restrict__ qgain, const float* __restrict__ kgain, float gain_eps) {
     __shared__ float cs[PREP_MAX];
     __shared__ float buf[8][PREP_MAX];
     lp_grid_release();
@@ -646,20 +648,32 @@ qkv_prepare_kernel(const float* __restrict__ qkv, int ld, const float* __restric
     }
     __syncthreads();
     const float* row = qkv + (long long)t * ld;
-    const long long page = page_table[(long long)seq_ids[t] * pt_stride + pos / page_size];
+    const long long page = G > 0 ? page_table[(long long)seq_ids[t] * pt_stride + pos / page_size] : 0;
     const int r = pos % page_size;
     for (int item = warp; item < H + 2 * G; item += 8) {
         if (item < H + G) {
             const int src = item * dk;               // query heads, then key heads, lie one after another
+            const float* gain = item < H ? qgain : kgain;
+            float pre = 1.0f;
+            if (gain) {
+                float s0 = 0.f;
+                for (int e = lane; e < dk; e += 32) {
+                    const float val = row[src + e] + (bias ? bias[src + e] : 0.f);
+                    s0 += val * val;
+                }
+                pre = 1.0f / sqrtf(lp_warp_sum(s0) / (float)dk + gain_eps);
+            }
             float ss = 0.f;
             for (int e = lane; e < dk; e += 32) {
                 float val = row[src + e] + (bias ? bias[src + e] : 0.f);
+                if (gain) val = val * pre * gain[e];
                 if (e < rd) {
                     int pair, partner;
                     bool first;
                     if (interleaved) { pair = e >> 1; first = !(e & 1); partner = e ^ 1; }
                     else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
-                    const float other = row[src + partner] + (bias ? bias[src + partner] : 0.f);
+                    float other = row[src + partner] + (bias ? bias[src + partner] : 0.f);
+                    if (gain) other = other * pre * gain[partner];
                     const float c = cs[2 * pair], s = cs[2 * pair + 1];
                     val = first ? val * c - other * s : val * c + other * s;
                 }
@@ -691,18 +705,19 @@ extern "C" int lp_qkv_prepare(const float* qkv, int ld, const float* bias, const
                               const int* seq_ids, const int* page_table, int pt_stride, void* q_out, int q_dtype,
                               void* pages, int kv_dtype, int T, int H, int G, int dk, int dv, int hdp, int rd,
                               int interleaved, int unit, float unit_eps, int page_size, float* zero, long long zero_count,
-                              cudaStream_t stream) {
+                              const float* qgain, const float* kgain, float gain_eps, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0) LP_REFUSE("qkv_prepare: %d / %d heads of %d and %d", H, G, dk, dv);
+    if (H <= 0 || G < 0 || dk <= 0 || dv <= 0) LP_REFUSE("qkv_prepare: %d / %d heads of %d and %d", H, G, dk, dv);
     if (hdp < dk || hdp < dv || dk > PREP_MAX) LP_REFUSE("qkv_prepare: heads of %d and %d stored in %d (at most %d)", dk, dv, hdp, PREP_MAX);
     if (rd < 0 || rd > dk || (rd & 1)) LP_REFUSE("qkv_prepare: rotary width %d for heads of %d", rd, dk);
     if (rd > 0 && !inv_freq) LP_REFUSE("qkv_prepare: a rotation without frequencies");
     if (ld < (H + G) * dk + G * dv) LP_REFUSE("qkv_prepare: rows of %d values for %d", ld, (H + G) * dk + G * dv);
-    if (page_size <= 0 || !pages) LP_REFUSE("qkv_prepare: needs the pages of the cache");
+    if (G > 0 && (page_size <= 0 || !pages)) LP_REFUSE("qkv_prepare: needs the pages of the cache");
+    if (G == 0) page_size = 1;
 #define LP_LAUNCH_PREP(TQ, TKV)                                                                                       \
     lp_launch(qkv_prepare_kernel<TQ, TKV>, T, 256, 0, stream, qkv, ld, bias, inv_freq, positions, seq_ids, page_table, \
               pt_stride, (TQ*)q_out, (TKV*)pages, H, G, dk, dv, hdp, rd, interleaved, unit, unit_eps, page_size, zero,  \
-              zero_count)
+              zero_count, qgain, kgain, gain_eps)
     if (q_dtype == LP_F32 && kv_dtype == LP_F32) LP_LAUNCH_PREP(float, float);
     else if (q_dtype == LP_BF16 && kv_dtype == LP_BF16) LP_LAUNCH_PREP(__nv_bfloat16, __nv_bfloat16);
     else LP_REFUSE("qkv_prepare: dtype codes q=%d kv=%d", q_dtype, kv_dtype);
@@ -713,12 +728,14 @@ extern "C" int lp_qkv_prepare(const float* qkv, int ld, const float* bias, const
 // ---------------------------------------------------------------- norm of a sublayer's result, residual sum, next norm
 // x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w   (the norm that follows a sublayer, then the residual sum), and, when
 // `w2` is given, out2[t] = x[t] / sqrt(mean(x[t]^2) + eps2) * w2 (the norm in front of the next sublayer) in the same
-// pass. One block per row; float32; sums in a fixed order.
+// pass. One block per row; float32; sums in a fixed order. Optional: `ybias` [d] is added to y first (the additive
+// vector of the sublayer's last map); `scale` [d] multiplies the normed result once more (a layer scale); `out2` without
+// `w2` receives the new x as it is (for a next sublayer that reads the stream itself, in its own number format).
 template <typename TOut>
 __global__ void __launch_bounds__(NORM_THREADS)
 post_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, float eps, float* __restrict__ x,
                      const float* __restrict__ w2, float eps2, TOut* __restrict__ out2, int d, float* __restrict__ zero,
-                     long long zero_count) {
+                     long long zero_count, const float* __restrict__ ybias, const float* __restrict__ scale) {
     __shared__ float scratch[32];
     lp_grid_release();
     lp_grid_wait();
@@ -727,14 +744,20 @@ post_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, f
     const float* yr = y + row * d;
     float* xr = x + row * d;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) ss += yr[i] * yr[i];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = yr[i] + (ybias ? ybias[i] : 0.f);
+        ss += v * v;
+    }
     ss = lp_block_sum(ss, scratch);
     const float f = 1.0f / sqrtf(ss / (float)d + eps);
     float ss2 = 0.f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = xr[i] + yr[i] * f * w[i];
+        float add = (yr[i] + (ybias ? ybias[i] : 0.f)) * f * w[i];
+        if (scale) add *= scale[i];
+        const float v = xr[i] + add;
         xr[i] = v;
         ss2 += v * v;
+        if (!w2 && out2) out2[row * d + i] = lp_from_float<TOut>(v);
     }
     if (!w2) return;
     ss2 = lp_block_sum(ss2, scratch);
@@ -748,7 +771,7 @@ template <typename TOut>
 __global__ void __launch_bounds__(NORM_THREADS)
 post_norm_add_vec4_kernel(const float* __restrict__ y, const float* __restrict__ w, float eps, float* __restrict__ x,
                           const float* __restrict__ w2, float eps2, TOut* __restrict__ out2, int d, float* __restrict__ zero,
-                          long long zero_count) {
+                          long long zero_count, const float* __restrict__ ybias, const float* __restrict__ scale) {
     __shared__ float scratch[32];
     lp_grid_release();
     lp_grid_wait();
@@ -757,21 +780,29 @@ post_norm_add_vec4_kernel(const float* __restrict__ y, const float* __restrict__
     const float4* yr = reinterpret_cast<const float4*>(y + row * d);
     float4* xr = reinterpret_cast<float4*>(x + row * d);
     const float4* wr = reinterpret_cast<const float4*>(w);
+    const float4* br = reinterpret_cast<const float4*>(ybias);
+    const float4* sr = reinterpret_cast<const float4*>(scale);
     const int quads = d >> 2;
     float ss = 0.f;
     for (int i = threadIdx.x; i < quads; i += blockDim.x) {
-        const float4 v = yr[i];
+        float4 v = yr[i];
+        if (br) { const float4 b = br[i]; v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
         ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     ss = lp_block_sum(ss, scratch);
     const float f = 1.0f / sqrtf(ss / (float)d + eps);
     float ss2 = 0.f;
     for (int i = threadIdx.x; i < quads; i += blockDim.x) {
-        const float4 v = yr[i], g = wr[i];
+        float4 v = yr[i];
+        const float4 g = wr[i];
+        if (br) { const float4 b = br[i]; v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
+        float4 a = make_float4(v.x * f * g.x, v.y * f * g.y, v.z * f * g.z, v.w * f * g.w);
+        if (sr) { const float4 c = sr[i]; a.x *= c.x; a.y *= c.y; a.z *= c.z; a.w *= c.w; }
         float4 r = xr[i];
-        r.x += v.x * f * g.x; r.y += v.y * f * g.y; r.z += v.z * f * g.z; r.w += v.w * f * g.w;
+        r.x += a.x; r.y += a.y; r.z += a.z; r.w += a.w;
         xr[i] = r;
         ss2 += r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w;
+        if (!w2 && out2) store4<TOut>(out2 + row * d + 4 * i, r.x, r.y, r.z, r.w);
     }
     if (!w2) return;
     ss2 = lp_block_sum(ss2, scratch);
@@ -786,21 +817,21 @@ post_norm_add_vec4_kernel(const float* __restrict__ y, const float* __restrict__
 
 extern "C" int lp_post_norm_add(const float* y, const float* w, float eps, float* x, const float* w2, float eps2,
                                 void* out2, int out2_dtype, int T, int d, float* zero, long long zero_count,
-                                cudaStream_t stream) {
+                                const float* ybias, const float* scale, cudaStream_t stream) {
     if (T <= 0 || d <= 0) return 0;
     if (w2 && !out2) LP_REFUSE("post_norm_add: a second norm without its output");
-    if (d % 4 == 0 && (((uintptr_t)y | (uintptr_t)x | (uintptr_t)w | (uintptr_t)w2 | (uintptr_t)out2) & 15) == 0) {
-        if (!w2 || out2_dtype == LP_F32)
-            lp_launch(post_norm_add_vec4_kernel<float>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (float*)out2, d, zero, zero_count);
+    if (d % 4 == 0 && (((uintptr_t)y | (uintptr_t)x | (uintptr_t)w | (uintptr_t)w2 | (uintptr_t)out2 | (uintptr_t)ybias | (uintptr_t)scale) & 15) == 0) {
+        if (!out2 || out2_dtype == LP_F32)
+            lp_launch(post_norm_add_vec4_kernel<float>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (float*)out2, d, zero, zero_count, ybias, scale);
         else if (out2_dtype == LP_BF16)
-            lp_launch(post_norm_add_vec4_kernel<__nv_bfloat16>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (__nv_bfloat16*)out2, d, zero, zero_count);
+            lp_launch(post_norm_add_vec4_kernel<__nv_bfloat16>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (__nv_bfloat16*)out2, d, zero, zero_count, ybias, scale);
         else LP_REFUSE("post_norm_add: output dtype code %d", out2_dtype);
         return lp_check_launch("post_norm_add");
     }
-    if (!w2 || out2_dtype == LP_F32)
-        lp_launch(post_norm_add_kernel<float>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (float*)out2, d, zero, zero_count);
+    if (!out2 || out2_dtype == LP_F32)
+        lp_launch(post_norm_add_kernel<float>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (float*)out2, d, zero, zero_count, ybias, scale);
     else if (out2_dtype == LP_BF16)
-        lp_launch(post_norm_add_kernel<__nv_bfloat16>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (__nv_bfloat16*)out2, d, zero, zero_count);
+        lp_launch(post_norm_add_kernel<__nv_bfloat16>, T, NORM_THREADS, 0, stream, y, w, eps, x, w2, eps2, (__nv_bfloat16*)out2, d, zero, zero_count, ybias, scale);
     else LP_REFUSE("post_norm_add: output dtype code %d", out2_dtype);
     return lp_check_launch("post_norm_add");
 }
@@ -885,4 +916,99 @@ extern "C" int lp_relu2(const float* z, int ldz, void* out, int out_dtype, int T
     else if (out_dtype == LP_BF16) lp_launch(relu2_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, (__nv_bfloat16*)out, T, F, zero, zero_count);
     else LP_REFUSE("relu2: output dtype code %d", out_dtype);
     return lp_check_launch("relu2");
+}
+
+// ---------------------------------------------------------------- gated activation of a dense feed-forward
+// out[t, f] = act(z[t, f] + b[f]) * (z[t, F + f] + b[F + f]) from the float32 sums of a stacked gate | up product
+// (z: rows of ldz values, the F gate sums first, then the F up sums; b: [2 F] or null). act: the tanh form of GELU,
+//     0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))),
+// evaluated in float32 (form 0), or the logistic form g / (1 + exp(-g)) (form 1).
+__device__ __forceinline__ float lp_gated_value(float g, float u, int form) {
+    if (form == 0) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    return g / (1.0f + expf(-g)) * u;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+gated_act_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, TOut* __restrict__ out, int T, int F,
+                 int form, float* __restrict__ zero, long long zero_count) {
+    lp_grid_release();
+    lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
+    const long long n = (long long)T * F;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / F;
+        const int f = (int)(i - t * F);
+        const float g = z[t * ldz + f] + (bias ? bias[f] : 0.f);
+        const float u = z[t * ldz + F + f] + (bias ? bias[F + f] : 0.f);
+        out[i] = lp_from_float<TOut>(lp_gated_value(g, u, form));
+    }
+}
+
+// The same, four values per thread (F and ldz multiples of four, 16-byte aligned pointers).
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+gated_act_vec4_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, TOut* __restrict__ out, int T,
+                      int F, int form, float* __restrict__ zero, long long zero_count) {
+    lp_grid_release();
+    lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
+    const int quads = F >> 2;
+    const long long n = (long long)T * quads;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / quads;
+        const int f = (int)(i - t * quads) * 4;
+        float4 g = *reinterpret_cast<const float4*>(z + t * ldz + f);
+        float4 u = *reinterpret_cast<const float4*>(z + t * ldz + F + f);
+        if (bias) {
+            const float4 bg = *reinterpret_cast<const float4*>(bias + f), bu = *reinterpret_cast<const float4*>(bias + F + f);
+            g.x += bg.x; g.y += bg.y; g.z += bg.z; g.w += bg.w;
+            u.x += bu.x; u.y += bu.y; u.z += bu.z; u.w += bu.w;
+        }
+        store4<TOut>(out + t * F + f, lp_gated_value(g.x, u.x, form), lp_gated_value(g.y, u.y, form),
+                     lp_gated_value(g.z, u.z, form), lp_gated_value(g.w, u.w, form));
+    }
+}
+
+extern "C" int lp_gated_act(const float* z, int ldz, const float* bias, void* out, int out_dtype, int T, int F, int form,
+                            float* zero, long long zero_count, cudaStream_t stream) {
+    if (T <= 0 || F <= 0) return 0;
+    if (ldz < 2 * F) LP_REFUSE("gated_act: rows of %d values for %d gate and %d up sums", ldz, F, F);
+    if (form < 0 || form > 1) LP_REFUSE("gated_act: form %d", form);
+    if (out_dtype != LP_F32 && out_dtype != LP_BF16) LP_REFUSE("gated_act: output dtype code %d", out_dtype);
+    const bool vec = F % 4 == 0 && ldz % 4 == 0 && (((uintptr_t)z | (uintptr_t)out | (uintptr_t)bias) & 15) == 0;
+    const long long n = vec ? (long long)T * (F / 4) : (long long)T * F;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (vec) {
+        if (out_dtype == LP_F32) lp_launch(gated_act_vec4_kernel<float>, (unsigned)blocks, 256, 0, stream, z, ldz, bias, (float*)out, T, F, form, zero, zero_count);
+        else lp_launch(gated_act_vec4_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, bias, (__nv_bfloat16*)out, T, F, form, zero, zero_count);
+    } else {
+        if (out_dtype == LP_F32) lp_launch(gated_act_kernel<float>, (unsigned)blocks, 256, 0, stream, z, ldz, bias, (float*)out, T, F, form, zero, zero_count);
+        else lp_launch(gated_act_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, bias, (__nv_bfloat16*)out, T, F, form, zero, zero_count);
+    }
+    return lp_check_launch("gated_act");
+}
+
+// ---------------------------------------------------------------- the stream in another number format
+// out[i] = x[i] for n float32 values (a sublayer that reads the stream itself takes it in its own format).
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+stream_cast_kernel(const float* __restrict__ x, TOut* __restrict__ out, long long n, float* __restrict__ zero, long long zero_count) {
+    lp_grid_release();
+    lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = lp_from_float<TOut>(x[i]);
+}
+
+extern "C" int lp_stream_cast(const float* x, void* out, int out_dtype, long long n, float* zero, long long zero_count,
+                              cudaStream_t stream) {
+    if (n <= 0) return 0;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (out_dtype == LP_F32) lp_launch(stream_cast_kernel<float>, (unsigned)blocks, 256, 0, stream, x, (float*)out, n, zero, zero_count);
+    else if (out_dtype == LP_BF16) lp_launch(stream_cast_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, x, (__nv_bfloat16*)out, n, zero, zero_count);
+    else LP_REFUSE("stream_cast: output dtype code %d", out_dtype);
+    return lp_check_launch("stream_cast");
 }

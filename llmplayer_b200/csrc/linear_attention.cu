@@ -7,7 +7,9 @@
 // The state is float32, one block per sequence (stored [H, dv, dk]), read at the start of a step and written
 // back at its end; decays, their logarithms and every sum are float32.
 //
-//   lp_gla_decay    a[t, c] = exp(-softplus(-z[t, c]) / tau), z from the low-rank factor's output
+//   lp_gla_decay    a[t, c] = exp(-softplus(-z[t, c]) / tau), z from the low-rank factor's output; or, for the
+//                   time-mixing family, a[t, c] = exp(-exp(z[t, c])) with z = A2 tanh(A1 x_t) + bias
+//   lp_token_shift  per token the blends x_t + (x_(t-1) - x_t) * mu_s that such a layer's maps read
 //   lp_gla_scan     the recurrence over a step's tokens, sequence by sequence, in token order
 //   lp_gla_finish   per head: RMS norm over dv (gain shared by heads), times silu(gate)
 #include "common.cuh"
@@ -19,7 +21,7 @@ namespace {
 template <typename TW>
 __global__ void __launch_bounds__(256)
 gla_decay_kernel(const float* __restrict__ low, int ldl, const TW* __restrict__ a2, const float* __restrict__ bias,
-                 float* __restrict__ out, int T, int C, int R, float inv_tau) {
+                 float* __restrict__ out, int T, int C, int R, float inv_tau, int form) {
     lp_grid_release();
     lp_grid_wait();
     const long long n = (long long)T * C;
@@ -29,6 +31,13 @@ gla_decay_kernel(const float* __restrict__ low, int ldl, const TW* __restrict__ 
         const float* x = low + t * ldl;
         const TW* w = a2 + (long long)c * R;
         float z = 0.f;
+        if (form == 1) {
+            // the time-mixing form: the factor's output passes through tanh, and the decay is exp(-exp(z))
+            for (int r = 0; r < R; ++r) z = fmaf(lp_to_float(w[r]), tanhf(x[r]), z);
+            z += bias ? bias[c] : 0.f;
+            out[i] = expf(-expf(z));
+            continue;
+        }
         for (int r = 0; r < R; ++r) z = fmaf(lp_to_float(w[r]), x[r], z);
         z += bias ? bias[c] : 0.f;
         // log sigmoid(z) = -softplus(-z)
@@ -57,7 +66,9 @@ constexpr int TB = 16;            // tokens per round of loads
 // Variants that other recurrences of this family need: `decay_per_head` (one decay per token and head, decay [T, H], for
 // all its key channels), `key_gain` [T, H] (the key of a token is multiplied by it: an input gate), and `ones` (the last of
 // the dv value columns is the constant 1 and the projection holds dv - 1 columns per head: that column of the state is
-// then the decayed sum of the gated keys, and its output their product with the query: a normaliser).
+// then the decayed sum of the gated keys, and its output their product with the query: a normaliser). `bonus` [H, dk]
+// (the time-mixing family): a token's output is formed from the state BEFORE the token plus u_c k_c v_j for the token
+// itself, o_t = (S_(t-1) + diag(u) k_t v_t^T)^T q_t, and the state is updated afterwards.
 constexpr int SCAN_WHOLE = 0, SCAN_LOCAL = 1, SCAN_OUTPUT = 2;
 
 template <int KP, int VT, int KPT, int JT>
@@ -66,7 +77,7 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
                 float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
                 float* __restrict__ out, int H, int dk, int dv, float q_scale, int mode, int chunks, int chunk,
                 float* __restrict__ chunk_state, float* __restrict__ chunk_decay, int decay_per_head,
-                const float* __restrict__ key_gain, int ones) {
+                const float* __restrict__ key_gain, int ones, const float* __restrict__ bonus) {
     extern __shared__ float sm[];
     float* qs = sm;                         // [TB][dk]
     float* ks = qs + TB * dk;
@@ -87,10 +98,11 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
     }
     float* S = mode == SCAN_WHOLE ? state + ((long long)slots[b] * H + h) * dv * dk
                                   : chunk_state + ((long long)blockIdx.z * H + h) * dv * dk;
-    float s[KPT][JT], prod[KPT];
+    float s[KPT][JT], prod[KPT], ub[KPT];
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
         const int c = part + KP * i;
+        ub[i] = (bonus && c < dk) ? bonus[(long long)h * dk + c] : 0.f;
 #pragma unroll
         for (int jj = 0; jj < JT; ++jj)
             s[i][jj] = (mode != SCAN_LOCAL && j0 + jj < dv && c < dk) ? S[(long long)(j0 + jj) * dk + c] : 0.f;
@@ -129,10 +141,19 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
                 if (c < dk) {
                     const float a = ai[c], k = ki[c], q = qi[c];
                     if (mode == SCAN_LOCAL) prod[u] *= a;
+                    if (bonus) {
 #pragma unroll
-                    for (int jj = 0; jj < JT; ++jj) {
-                        s[u][jj] = fmaf(a, s[u][jj], k * v[jj]);
-                        acc[jj] = fmaf(s[u][jj], q, acc[jj]);
+                        for (int jj = 0; jj < JT; ++jj) {
+                            const float kv = k * v[jj];
+                            acc[jj] = fmaf(fmaf(ub[u], kv, s[u][jj]), q, acc[jj]);
+                            s[u][jj] = fmaf(a, s[u][jj], kv);
+                        }
+                    } else {
+#pragma unroll
+                        for (int jj = 0; jj < JT; ++jj) {
+                            s[u][jj] = fmaf(a, s[u][jj], k * v[jj]);
+                            acc[jj] = fmaf(s[u][jj], q, acc[jj]);
+                        }
                     }
                 }
             }
@@ -256,6 +277,33 @@ exp_gates_kernel(const float* __restrict__ proj, int ld, int i_off, int f_off, c
     if (tid == 0) *mp = carry;
 }
 
+
+// ---------------------------------------------------------------- token shift
+// For the S maps of a time-mixing layer: out[s][t] = x_t + (x_(t-1) - x_t) * mu[s], where x_(t-1) of a sequence's first
+// new token is the row kept for its slot in `last` (zeros at the sequence's start). One block per token; the block of a
+// sequence's first new token alone reads that row, and, having read it, puts the sequence's last new token there.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+token_shift_kernel(const float* __restrict__ x, float* __restrict__ last, const float* __restrict__ mu, const int* __restrict__ slots,
+                   const int* __restrict__ q_start, const int* __restrict__ seq_ids, TOut* __restrict__ out, int T, int d, int S) {
+    lp_grid_release();
+    lp_grid_wait();
+    const int t = blockIdx.x;
+    const int b = seq_ids[t];
+    const int t0 = q_start[b], t1 = q_start[b + 1];
+    const bool first = t == t0;
+    float* kept = last + (long long)slots[b] * d;
+    const float* cur = x + (long long)t * d;
+    const float* prev = first ? kept : cur - d;
+    const float* newest = x + (long long)(t1 - 1) * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float c = cur[i], p = prev[i];
+        if (first) kept[i] = newest[i];          // this thread has read kept[i]; no other block reads or writes it
+        for (int s = 0; s < S; ++s)
+            out[((long long)s * T + t) * d + i] = lp_from_float<TOut>(fmaf(p - c, mu[(long long)s * d + i], c));
+    }
+}
+
 // ---------------------------------------------------------------- finish
 // out[t, h * dv + j] = o[t, h, j] / sqrt(mean_j o^2 + eps) * gain[j] * silu(gate[t, h * dv + j]); a warp per (t, h).
 // Variants: rows of o that are `xs` apart (xs > dv: further columns follow a head's values), a gain per head
@@ -294,18 +342,21 @@ gla_finish_kernel(const float* __restrict__ o, const float* __restrict__ gain, f
 
 }  // namespace
 
+// form 0: sigmoid(z)^(1 / tau) with z = a2 low + bias; form 1: exp(-exp(z)) with z = a2 tanh(low) + bias (tau unused).
 extern "C" int lp_gla_decay(const float* low, int ldl, const void* a2, int w_dtype, const float* bias, float* out,
-                            int T, int C, int R, float tau, cudaStream_t stream) {
+                            int T, int C, int R, float tau, int form, cudaStream_t stream) {
     if (T <= 0 || C <= 0) return 0;
     if (R <= 0 || ldl < R) LP_REFUSE("gla_decay: a factor of %d values in rows of %d", R, ldl);
+    if (form < 0 || form > 1) LP_REFUSE("gla_decay: form %d", form);
+    if (form == 1) tau = 1.0f;
     if (!(tau > 0.f)) LP_REFUSE("gla_decay: temperature %g", (double)tau);
     const long long n = (long long)T * C;
     long long blocks = (n + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (w_dtype == LP_F32)
-        lp_launch(gla_decay_kernel<float>, (unsigned)blocks, 256, 0, stream, low, ldl, (const float*)a2, bias, out, T, C, R, 1.0f / tau);
+        lp_launch(gla_decay_kernel<float>, (unsigned)blocks, 256, 0, stream, low, ldl, (const float*)a2, bias, out, T, C, R, 1.0f / tau, form);
     else if (w_dtype == LP_BF16)
-        lp_launch(gla_decay_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, low, ldl, (const __nv_bfloat16*)a2, bias, out, T, C, R, 1.0f / tau);
+        lp_launch(gla_decay_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, low, ldl, (const __nv_bfloat16*)a2, bias, out, T, C, R, 1.0f / tau, form);
     else LP_REFUSE("gla_decay: weight dtype code %d", w_dtype);
     return lp_check_launch("gla_decay");
 }
@@ -317,7 +368,7 @@ extern "C" int lp_gla_decay(const float* low, int ldl, const void* a2, int w_dty
 extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay, float* state,
                            const int* slots, const int* q_start, float* out, int B, int H, int dk, int dv,
                            float q_scale, int chunks, int chunk, float* chunk_state, float* chunk_decay,
-                           int decay_per_head, const float* key_gain, int ones, cudaStream_t stream) {
+                           int decay_per_head, const float* key_gain, int ones, const float* bonus, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (chunks < 1) chunks = 1;
     ones = ones ? 1 : 0;
@@ -339,17 +390,17 @@ extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
         if (chunks == 1) {                                                                                            \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_WHOLE, 1, 0, (float*)nullptr,       \
-                      (float*)nullptr, decay_per_head, key_gain, ones);                                                                               \
+                      (float*)nullptr, decay_per_head, key_gain, ones, bonus);                                                                               \
         } else {                                                                                                      \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_LOCAL, chunks, chunk, chunk_state,  \
-                      chunk_decay, decay_per_head, key_gain, ones);                                                                                   \
+                      chunk_decay, decay_per_head, key_gain, ones, bonus);                                                                                   \
             const long long per = (long long)H * dv * dk;                                                             \
             lp_launch(gla_combine_kernel, dim3((unsigned)((per + 255) / 256), B), 256, 0, stream, state, slots,       \
                       q_start, chunk_state, (const float*)chunk_decay, H, dk, dv, chunks, chunk);                     \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_OUTPUT, chunks, chunk, chunk_state, \
-                      chunk_decay, decay_per_head, key_gain, ones);                                                                                   \
+                      chunk_decay, decay_per_head, key_gain, ones, bonus);                                                                                   \
         }                                                                                                             \
     } while (0)
     // few key channels: 4 threads per column, 64 columns per CTA; from 32 channels on: 16 threads per column, 16 columns
@@ -393,4 +444,15 @@ extern "C" int lp_exp_gates(const float* proj, int ld, int i_off, int f_off, con
     lp_launch(exp_gates_kernel, dim3(B, H), 256, 0, stream, proj, ld, i_off, f_off, bias_i, bias_f, cap, mstate, slots, q_start,
               decay, gain, max_row, H);
     return lp_check_launch("exp_gates");
+}
+
+// x: float32 [T, d]; last: float32 [slots, d]; mu: float32 [S, d]; out: [S, T, d] float32 or bfloat16.
+extern "C" int lp_token_shift(const float* x, float* last, const float* mu, const int* slots, const int* q_start,
+                              const int* seq_ids, void* out, int out_dtype, int T, int d, int S, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d <= 0 || S <= 0) LP_REFUSE("token_shift: rows of %d values, %d blends", d, S);
+    if (out_dtype == LP_F32) lp_launch(token_shift_kernel<float>, T, 256, 0, stream, x, last, mu, slots, q_start, seq_ids, (float*)out, T, d, S);
+    else if (out_dtype == LP_BF16) lp_launch(token_shift_kernel<__nv_bfloat16>, T, 256, 0, stream, x, last, mu, slots, q_start, seq_ids, (__nv_bfloat16*)out, T, d, S);
+    else LP_REFUSE("token_shift: output dtype code %d", out_dtype);
+    return lp_check_launch("token_shift");
 }

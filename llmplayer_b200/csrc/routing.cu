@@ -112,6 +112,78 @@ expert_scale_vec8_kernel(__nv_bfloat16* __restrict__ hidden, int ldh, const floa
     }
 }
 
+
+// Another rule: the `top` experts with the largest logits z[e] + bias[e] are chosen, and their weights are the softmax
+// over the chosen logits alone. A warp per token; among equal logits the expert with the lower index wins. `extra`
+// further columns of z (beyond the E logits) are gates of experts that every token uses: weights[t, E + i] =
+// sigmoid(z[t, E + i]).
+__global__ void __launch_bounds__(128)
+route_top_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ bias, float* __restrict__ weights, int ldw,
+                 int T, int E, int top, int extra) {
+    extern __shared__ float sm[];
+    lp_grid_release();
+    lp_grid_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long t = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    float* s = sm + (size_t)warp * 2 * E;
+    float* w = s + E;
+    for (int e = lane; e < E; e += 32) {
+        s[e] = z[t * ldz + e] + (bias ? bias[e] : 0.f);
+        w[e] = 0.f;
+    }
+    __syncwarp();
+    float big = 0.f, sum = 0.f;
+    for (int n = 0; n < top; ++n) {
+        // the largest logit not yet chosen: each lane over its experts, then over the lanes (lower index wins a tie)
+        float bv = -INFINITY;
+        int best = E;
+        for (int e = lane; e < E; e += 32)
+            if (w[e] == 0.f && s[e] > bv) { bv = s[e]; best = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best, o);
+            if (ov > bv || (ov == bv && oe < best)) { bv = ov; best = oe; }
+        }
+        if (best >= E) break;
+        if (n == 0) big = bv;
+        const float p = expf(bv - big);
+        sum += p;
+        if (lane == 0) w[best] = p;
+        __syncwarp();
+    }
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) weights[t * ldw + e] = w[e] * inv;
+    for (int i = lane; i < extra; i += 32) weights[t * ldw + E + i] = 1.0f / (1.0f + expf(-z[t * ldz + E + i]));
+}
+
+// Hidden activations of clamped gated experts from the float32 sums of ONE stacked product over all experts:
+// z[t] = [ gate sums of all experts (total) | up sums of all experts (total) ]. With g = min(gate, limit) and
+// u = clamp(up, -limit, limit):  hidden[t, c] = g * sigmoid(1.702 g) * (u + 1) * weights[t, expert of c].
+// Columns below E * ff belong to expert c / ff and take `limit`; the columns beyond belong to one more expert (index E)
+// with `limit_rest`. weights null: no scaling.
+template <typename TH>
+__global__ void __launch_bounds__(256)
+expert_act_kernel(const float* __restrict__ z, int ldz, int total, TH* __restrict__ hidden, const float* __restrict__ weights,
+                  int ldw, int T, int E, int ff, float limit, float limit_rest, float* __restrict__ zero, long long zero_count) {
+    lp_grid_release();
+    lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
+    const long long n = (long long)T * total;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / total;
+        const int c = (int)(i - t * total);
+        const int e = c < E * ff ? c / ff : E;
+        const float lim = e < E ? limit : limit_rest;
+        const float g = fminf(z[t * ldz + c], lim);
+        const float u = fminf(fmaxf(z[t * ldz + total + c], -lim), lim);
+        float v = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+        if (weights) v *= weights[t * ldw + e];
+        hidden[i] = lp_from_float<TH>(v);
+    }
+}
+
 }  // namespace
 
 // z: float32 [T, ldz] (E logits per row); weights: float32 [T, ldw], E values per row written.
@@ -148,4 +220,34 @@ extern "C" int lp_expert_scale(void* hidden, int dtype, int ldh, const float* we
     else if (dtype == LP_BF16) lp_launch(expert_scale_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, (__nv_bfloat16*)hidden, ldh, weights, ldw, T, E, ff, zero, zero_count);
     else LP_REFUSE("expert_scale: dtype code %d", dtype);
     return lp_check_launch("expert_scale");
+}
+
+// z: float32 [T, ldz] (E logits per row, then `extra` gate columns); bias: float32 [E] or null; weights: float32
+// [T, ldw], E + extra values per row written.
+extern "C" int lp_route_top(const float* z, int ldz, const float* bias, float* weights, int ldw, int T, int E, int top,
+                            int extra, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E || extra < 0) LP_REFUSE("route_top: %d of %d experts, %d gates", top, E, extra);
+    if (ldz < E + extra || ldw < E + extra) LP_REFUSE("route_top: rows of %d and %d values for %d columns", ldz, ldw, E + extra);
+    const size_t smem = (size_t)4 * 2 * E * sizeof(float);
+    if (smem > 48 * 1024) LP_REFUSE("route_top: %d experts need %zu bytes of shared memory", E, smem);
+    lp_launch(route_top_kernel, (unsigned)((T + 3) / 4), 128, smem, stream, z, ldz, bias, weights, ldw, T, E, top, extra);
+    return lp_check_launch("route_top");
+}
+
+// z: float32 [T, ldz] with the gate sums of `total` hidden columns, then their up sums; hidden: [T, total].
+extern "C" int lp_expert_act(const float* z, int ldz, int total, void* hidden, int dtype, const float* weights, int ldw,
+                             int T, int E, int ff, float limit, float limit_rest, float* zero, long long zero_count,
+                             cudaStream_t stream) {
+    if (T <= 0 || total <= 0) return 0;
+    if (E < 0 || ff <= 0 || (long long)E * ff > total) LP_REFUSE("expert_act: %d experts of %d in %d columns", E, ff, total);
+    if (ldz < 2 * total) LP_REFUSE("expert_act: rows of %d values for 2 x %d sums", ldz, total);
+    if (weights && ldw < E + (total > E * ff ? 1 : 0)) LP_REFUSE("expert_act: rows of %d weights", ldw);
+    const long long n = (long long)T * total;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == LP_F32) lp_launch(expert_act_kernel<float>, (unsigned)blocks, 256, 0, stream, z, ldz, total, (float*)hidden, weights, ldw, T, E, ff, limit, limit_rest, zero, zero_count);
+    else if (dtype == LP_BF16) lp_launch(expert_act_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, total, (__nv_bfloat16*)hidden, weights, ldw, T, E, ff, limit, limit_rest, zero, zero_count);
+    else LP_REFUSE("expert_act: dtype code %d", dtype);
+    return lp_check_launch("expert_act");
 }

@@ -32,14 +32,18 @@ _SIGNATURES = {
         "lp_advance": [_P, _P, _P, _P, _I, _P],
         "lp_rope_angles": [_P, _P, _P, _I, _I, _P],
         "lp_qkv_prepare": [_P, _I, _P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P,
-                           ctypes.c_longlong, _P],
-        "lp_post_norm_add": [_P, _P, _F, _P, _P, _F, _P, _I, _I, _I, _P, ctypes.c_longlong, _P],
+                           ctypes.c_longlong, _P, _P, _F, _P],
+        "lp_post_norm_add": [_P, _P, _F, _P, _P, _F, _P, _I, _I, _I, _P, ctypes.c_longlong, _P, _P, _P],
+        "lp_gated_act": [_P, _I, _P, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
+        "lp_stream_cast": [_P, _P, _I, ctypes.c_longlong, _P, ctypes.c_longlong, _P],
         "lp_stream_add": [_P, _P, _P, _I, _I, _P],
         "lp_relu2": [_P, _I, _P, _I, _I, _I, _P, ctypes.c_longlong, _P],
     },
     "routing": {
         "lp_route": [_P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
         "lp_expert_scale": [_P, _I, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
+        "lp_route_top": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+        "lp_expert_act": [_P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P, ctypes.c_longlong, _P],
     },
     "gemm_plain": {
         "lp_gemm_plain": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -78,8 +82,9 @@ _SIGNATURES = {
         "lp_latent_expand": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
     },
     "linear_attention": {
-        "lp_gla_decay": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _F, _P],
-        "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _I, _P],
+        "lp_gla_decay": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _F, _I, _P],
+        "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _I, _P, _P],
+        "lp_token_shift": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "lp_gla_finish": [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _I, _I, _I, _P, _P],
         "lp_exp_gates": [_P, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _P],
     },
@@ -423,6 +428,16 @@ def _slice(t: torch.Tensor, what: str):
     return t.data_ptr(), int(t.stride(0))
 
 
+def _out_matrix(t: torch.Tensor, what: str):
+    """(pointer, row stride) of a product's output: a matrix whose columns lie together; it may be a column slice of a
+    wider one, so that several products write side by side into one buffer."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dim() != 2:
+        raise KernelError(f"{what}: expected a CUDA matrix")
+    if t.shape[1] > 1 and t.stride(1) != 1:
+        raise KernelError(f"{what}: columns must lie together, got strides {t.stride()}")
+    return t.data_ptr(), int(t.stride(0)) if t.shape[0] > 1 or t.stride(0) >= t.shape[1] else int(t.shape[1])
+
+
 def _clear_args(clear: Optional[torch.Tensor], what: str):
     """(pointer, count) of a float32 buffer that a kernel zeroes on the side, or (None, 0)."""
     if clear is None:
@@ -610,15 +625,15 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = 
     """
     _want(a, "gemm a", ndim=2)
     _want(w, "gemm w", ndim=2)
-    _want(out, "gemm out", ndim=2)
+    out_ptr, ldc = _out_matrix(out, "gemm out")
     M, K = a.shape
     N = out.shape[1]
     rows = 2 * N if mode == SWIGLU else N
     if w.shape != (rows, K) or out.shape[0] != M:
         raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, mode {mode}")
     lib = library("gemm_plain")
-    _check(lib, lib.lp_gemm_plain(a.data_ptr(), _code(a, "gemm a"), w.data_ptr(), _code(w, "gemm w"), out.data_ptr(),
-                                  _code(out, "gemm out"), M, N, K, K, K, N, mode, _stream()))
+    _check(lib, lib.lp_gemm_plain(a.data_ptr(), _code(a, "gemm a"), w.data_ptr(), _code(w, "gemm w"), out_ptr,
+                                  _code(out, "gemm out"), M, N, K, K, K, ldc, mode, _stream()))
     return out
 
 
@@ -727,7 +742,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
     """
     _want(a, "gemm a", torch.bfloat16, 2)
     _want(w, "gemm w", torch.bfloat16, 2)
-    _want(out, "gemm out", ndim=2)
+    out_ptr, ldc = _out_matrix(out, "gemm out")          # may be a column slice of a wider buffer
     M, K = a.shape
     N = out.shape[1]
     rows = 128 * (-(-N // 64)) if mode == SWIGLU else N
@@ -735,6 +750,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
         raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, mode {mode}")
     if M == 0:
         return out
+    if ldc != N and norm_after is not None:
+        raise KernelError("gemm: a following norm needs an output of whole rows")
     lib = library("gemm_tcgen05")
     status = kernel_status()
     if (M >= PERSISTENT_MIN_TOKENS and not block_tok and not splits and norm_after is None
@@ -742,8 +759,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
         # many tokens: one CTA per SM walks over the tiles, epilogue and MMAs of neighbouring tiles overlap
         if mode == ACCUMULATE and out.dtype != torch.float32:
             raise KernelError("gemm: accumulation needs a float32 output")
-        _check(lib, lib.lp_gemm_persistent(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
-                                           K, K, N, mode, status.data_ptr(), _stream()))
+        _check(lib, lib.lp_gemm_persistent(a.data_ptr(), w.data_ptr(), out_ptr, _code(out, "gemm out"), M, N, K,
+                                           K, K, ldc, mode, status.data_ptr(), _stream()))
         return out
     tile, n_splits = gemm_plan(M, N, K, mode)
     tile = block_tok or tile
@@ -770,8 +787,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
         _want(counter, "gemm norm counter", torch.int32, 1)
         norm_args = (gain.data_ptr(), float(eps), normed.data_ptr(), _ptr(clear),
                      clear.numel() if clear is not None else 0, counter.data_ptr())
-    _check(lib, lib.lp_gemm_tcgen05(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
-                                    K, K, N, mode, tile, n_splits, status.data_ptr(), *norm_args, _stream()))
+    _check(lib, lib.lp_gemm_tcgen05(a.data_ptr(), w.data_ptr(), out_ptr, _code(out, "gemm out"), M, N, K,
+                                    K, K, ldc, mode, tile, n_splits, status.data_ptr(), *norm_args, _stream()))
     return out
 
 
@@ -1222,9 +1239,11 @@ def latent_expand(partials: torch.Tensor, v_up: torch.Tensor, gate: Optional[tor
 
 
 # --------------------------------------------------------------------------- gated linear attention
-def gla_decay(low: torch.Tensor, up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, tau: float) -> torch.Tensor:
+def gla_decay(low: torch.Tensor, up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, tau: float = 1.0,
+              double_exp: bool = False) -> torch.Tensor:
     """out[t, c] = sigmoid(up[c] . low[t] + bias[c]) ** (1 / tau), float32; ``low``: float32 [T, R] (may be a column
-    slice), ``up``: [C, R]."""
+    slice), ``up``: [C, R]. ``double_exp``: out[t, c] = exp(-exp(up[c] . tanh(low[t]) + bias[c])) instead (the decay of
+    the time-mixing family)."""
     lp, ldl = _slice(low, "gla_decay low")
     _want(up, "gla_decay up", ndim=2)
     _want(out, "gla_decay out", torch.float32, 2)
@@ -1238,7 +1257,7 @@ def gla_decay(low: torch.Tensor, up: torch.Tensor, bias: Optional[torch.Tensor],
             raise KernelError(f"gla_decay: a bias of {bias.numel()} values for {C} channels")
     lib = library("linear_attention")
     _check(lib, lib.lp_gla_decay(lp, ldl, up.data_ptr(), _code(up, "gla_decay up"), _ptr(bias), out.data_ptr(), T, C, R,
-                                 float(tau), _stream()))
+                                 float(tau), 1 if double_exp else 0, _stream()))
     return out
 
 
@@ -1249,7 +1268,8 @@ GLA_CHUNKED_FROM = 256        # from how many new tokens of a sequence on the ch
 def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor,
              slots: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, *, num_heads: int, key_dim: int,
              value_dim: int, q_scale: float, max_new: int = 0, scratch=None, decay_per_head: bool = False,
-             key_gain: Optional[torch.Tensor] = None, ones_column: bool = False) -> torch.Tensor:
+             key_gain: Optional[torch.Tensor] = None, ones_column: bool = False,
+             bonus: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The recurrence S <- diag(decay_t) S + k_t v_t^T, out_t = S^T (q_t * q_scale) over the step's tokens of every
     sequence, from and into ``state`` float32 [slots, H, dv, dk] (row ``slots[b]`` for sequence b; a value column's
     key channels lie together). ``proj``: float32
@@ -1261,7 +1281,9 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
     ``decay_per_head``: ``decay`` is float32 [T, H], one decay per token and head for all its key channels.
     ``key_gain``: float32 [T, H], multiplied into the token's keys (an input gate). ``ones_column``: the last of the
     ``value_dim`` columns of state and output is fed the constant 1 instead of a value (the projection then holds
-    ``value_dim - 1`` values per head): its output is q . (decayed sum of the gated keys), a normaliser."""
+    ``value_dim - 1`` values per head): its output is q . (decayed sum of the gated keys), a normaliser.
+    ``bonus``: float32 [H, dk]; a token's output then comes from the state BEFORE the token plus bonus_c k_c v_j for the
+    token itself, out_t = (S + diag(bonus) k_t v_t^T)^T q_t, and the state is updated afterwards."""
     _want(proj, "gla_scan proj", torch.float32, 2)
     _want(decay, "gla_scan decay", torch.float32, 2)
     _want(state, "gla_scan state", torch.float32, 4)
@@ -1271,6 +1293,10 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
     T = proj.shape[0]
     H, dk, dv = num_heads, key_dim, value_dim
     B = slots.numel()
+    if bonus is not None:
+        _want(bonus, "gla_scan bonus", torch.float32, 2)
+        if bonus.shape != (H, dk):
+            raise KernelError(f"gla_scan: a bonus of {tuple(bonus.shape)} for {H} heads of {dk} channels")
     if key_gain is not None:
         _want(key_gain, "gla_scan key_gain", torch.float32, 2)
         if key_gain.shape != (T, H):
@@ -1288,7 +1314,7 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
     _check(lib, lib.lp_gla_scan(proj.data_ptr(), proj.shape[1], int(q_off), int(k_off), int(v_off), decay.data_ptr(),
                                 state.data_ptr(), slots.data_ptr(), q_start.data_ptr(), out.data_ptr(), B, H, dk, dv,
                                 float(q_scale), chunks, GLA_CHUNK, _ptr(chunk_state), _ptr(chunk_decay),
-                                1 if decay_per_head else 0, _ptr(key_gain), 1 if ones_column else 0, _stream()))
+                                1 if decay_per_head else 0, _ptr(key_gain), 1 if ones_column else 0, _ptr(bonus), _stream()))
     if chunks > 1:
         count_launches(2)
     return out
@@ -1354,15 +1380,41 @@ def exp_gates(proj: torch.Tensor, i_off: int, f_off: int, bias_i: Optional[torch
                                  decay.data_ptr(), gain.data_ptr(), max_row.data_ptr(), B, H, _stream()))
 
 
+def token_shift(x: torch.Tensor, last: torch.Tensor, mu: torch.Tensor, slots: torch.Tensor, q_start: torch.Tensor,
+                seq_ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[s, t] = x[t] + (x[t - 1] - x[t]) * mu[s] for the S rows of ``mu`` (float32 [S, d]); the token before a
+    sequence's first new token is the row of its slot in ``last`` (float32 [slots, d]), which then receives the
+    sequence's last new token. ``x``: float32 [T, d]; ``out``: [S, T, d]."""
+    _want(x, "token_shift x", torch.float32, 2)
+    _want(last, "token_shift last", torch.float32, 2)
+    _want(mu, "token_shift mu", torch.float32, 2)
+    _want(slots, "token_shift slots", torch.int32, 1)
+    _want(q_start, "token_shift q_start", torch.int32, 1)
+    _want(seq_ids, "token_shift seq_ids", torch.int32, 1)
+    _want(out, "token_shift out", ndim=3)
+    T, d = x.shape
+    S = mu.shape[0]
+    if last.shape[1] != d or mu.shape[1] != d or out.shape != (S, T, d) or seq_ids.numel() != T or q_start.numel() != slots.numel() + 1:
+        raise KernelError(f"token_shift: x {tuple(x.shape)}, last {tuple(last.shape)}, mu {tuple(mu.shape)}, out {tuple(out.shape)}")
+    lib = library("linear_attention")
+    _check(lib, lib.lp_token_shift(x.data_ptr(), last.data_ptr(), mu.data_ptr(), slots.data_ptr(), q_start.data_ptr(),
+                                   seq_ids.data_ptr(), out.data_ptr(), _code(out, "token_shift out"), T, d, S, _stream()))
+    return out
+
+
 # --------------------------------------------------------------------------- general attention heads, sublayer norms
 def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], rotation: Rotation, positions: torch.Tensor,
                 seq_ids: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor, pages: torch.Tensor, *,
                 num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, unit_norm_eps: Optional[float],
-                clear: Optional[torch.Tensor] = None) -> None:
+                clear: Optional[torch.Tensor] = None, q_gain: Optional[torch.Tensor] = None,
+                k_gain: Optional[torch.Tensor] = None, gain_eps: float = 0.0, write_kv: bool = True) -> None:
     """From the float32 projection ``qkv`` [T, H * dk + G * dk + G * dv]: add ``bias`` (float32, same width, or None),
     rotate queries and keys, divide each query and key head by its root mean square (``unit_norm_eps`` not None), and
     store queries to ``q_out`` [T, H * hdp] and keys and values into ``pages`` [num_pages, 2, G, page_size, hdp], every
-    head padded with zeros to the pages' head size hdp."""
+    head padded with zeros to the pages' head size hdp. ``q_gain`` / ``k_gain`` (float32 [dk], shared by the heads):
+    before the rotation, query / key heads are RMS-normed over dk with that gain and ``gain_eps``. ``write_kv=False``:
+    ``qkv`` [T, H * dk] holds queries only (a layer that attends over another layer's keys and values); ``pages`` only
+    says how queries are stored."""
     _want(qkv, "qkv_prepare qkv", torch.float32, 2)
     _want(positions, "qkv_prepare positions", torch.int32, 1)
     _want(seq_ids, "qkv_prepare seq_ids", torch.int32, 1)
@@ -1372,8 +1424,17 @@ def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], rotation: Rotat
     T = qkv.shape[0]
     H, G, dk, dv = num_heads, num_kv_heads, key_dim, value_dim
     hdp = pages.shape[4]
+    if pages.shape[1] != 2 or pages.shape[2] != G:
+        raise KernelError(f"qkv_prepare: pages {tuple(pages.shape)} for {G} key heads")
+    if not write_kv:
+        G = 0
     F = (H + G) * dk + G * dv
-    if qkv.shape[1] != F or q_out.shape != (T, H * hdp) or pages.shape[1] != 2 or pages.shape[2] != G:
+    for name, gain in (("q_gain", q_gain), ("k_gain", k_gain)):
+        if gain is not None:
+            _want(gain, f"qkv_prepare {name}", torch.float32, 1)
+            if gain.numel() != dk:
+                raise KernelError(f"qkv_prepare: {name} of {gain.numel()} values for heads of {dk}")
+    if qkv.shape[1] != F or q_out.shape != (T, H * hdp):
         raise KernelError(f"qkv_prepare: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}, pages {tuple(pages.shape)}")
     if bias is not None:
         _want(bias, "qkv_prepare bias", torch.float32, 1)
@@ -1383,16 +1444,19 @@ def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], rotation: Rotat
     lib = library("elementwise")
     _check(lib, lib.lp_qkv_prepare(
         qkv.data_ptr(), qkv.shape[1], _ptr(bias), freq_ptr, positions.data_ptr(), seq_ids.data_ptr(),
-        page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(), _code(q_out, "qkv_prepare q_out"), pages.data_ptr(),
-        _code(pages, "qkv_prepare pages"), T, H, G, dk, dv, hdp, rotary_dim, interleaved,
+        page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(), _code(q_out, "qkv_prepare q_out"),
+        pages.data_ptr() if write_kv else None, _code(pages, "qkv_prepare pages"), T, H, G, dk, dv, hdp, rotary_dim, interleaved,
         0 if unit_norm_eps is None else 1, float(unit_norm_eps or 0.0), pages.shape[3], *_clear_args(clear, "qkv_prepare"),
-        _stream()))
+        _ptr(q_gain), _ptr(k_gain) if write_kv else None, float(gain_eps), _stream()))
 
 
 def post_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor, *, next_weight: Optional[torch.Tensor] = None,
-                  next_eps: float = 0.0, next_out: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  next_eps: float = 0.0, next_out: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None,
+                  y_bias: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x += y / sqrt(mean(y^2) + eps) * weight, float32 in place; with ``next_weight``, also
-    next_out = x / sqrt(mean(x^2) + next_eps) * next_weight of the new x (the norm in front of the next sublayer)."""
+    next_out = x / sqrt(mean(x^2) + next_eps) * next_weight of the new x (the norm in front of the next sublayer).
+    ``y_bias`` (float32 [d]) is added to y first; ``scale`` (float32 [d]) multiplies the normed y once more (a layer
+    scale); ``next_out`` without ``next_weight`` receives the new x as it is, in ``next_out``'s number format."""
     _want(y, "post_norm_add y", torch.float32, 2)
     _want(x, "post_norm_add x", torch.float32, 2)
     _want(weight, "post_norm_add weight", torch.float32, 1)
@@ -1402,15 +1466,58 @@ def post_norm_add(y: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Te
     code = F32
     if next_weight is not None:
         _want(next_weight, "post_norm_add next_weight", torch.float32, 1)
+        if next_weight.numel() != d or next_out is None:
+            raise KernelError("post_norm_add: a next norm needs its gain over whole rows and its output")
+    if next_out is not None:
         _want(next_out, "post_norm_add next_out", ndim=2)
-        if next_weight.numel() != d or next_out.shape != x.shape:
-            raise KernelError(f"post_norm_add: next norm {tuple(next_weight.shape)} into {tuple(next_out.shape)}")
+        if next_out.shape != x.shape:
+            raise KernelError(f"post_norm_add: next output {tuple(next_out.shape)} for x {tuple(x.shape)}")
         code = _code(next_out, "post_norm_add next_out")
+    for name, vec in (("y_bias", y_bias), ("scale", scale)):
+        if vec is not None:
+            _want(vec, f"post_norm_add {name}", torch.float32, 1)
+            if vec.numel() != d:
+                raise KernelError(f"post_norm_add: {name} of {vec.numel()} values for rows of {d}")
     lib = library("elementwise")
     _check(lib, lib.lp_post_norm_add(y.data_ptr(), weight.data_ptr(), float(eps), x.data_ptr(), _ptr(next_weight),
-                                     float(next_eps), _ptr(next_out) if next_weight is not None else None, code, T, d,
-                                     *_clear_args(clear, "post_norm_add"), _stream()))
+                                     float(next_eps), _ptr(next_out), code, T, d,
+                                     *_clear_args(clear, "post_norm_add"), _ptr(y_bias), _ptr(scale), _stream()))
     return x
+
+
+def gated_act(z: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, form: str = "gelu_tanh",
+              clear: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, f] = act(z[t, f] + bias[f]) * (z[t, F + f] + bias[F + f]) from the float32 sums ``z`` [T, 2 F] of a stacked
+    gate | up product (may be a column slice); ``bias``: float32 [2 F] or None. ``form``: ``"gelu_tanh"``
+    (0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))) or ``"silu"``. Everything in float32 until ``out`` is stored."""
+    zp, ldz = _slice(z, "gated_act z")
+    _want(out, "gated_act out", ndim=2)
+    T, F = out.shape
+    if z.shape != (T, 2 * F):
+        raise KernelError(f"gated_act: z {tuple(z.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _want(bias, "gated_act bias", torch.float32, 1)
+        if bias.numel() != 2 * F:
+            raise KernelError(f"gated_act: a bias of {bias.numel()} values for 2 x {F} sums")
+    forms = {"gelu_tanh": 0, "silu": 1}
+    if form not in forms:
+        raise KernelError(f"gated_act: unknown form {form!r}")
+    lib = library("elementwise")
+    _check(lib, lib.lp_gated_act(zp, ldz, _ptr(bias), out.data_ptr(), _code(out, "gated_act out"), T, F, forms[form],
+                                 *_clear_args(clear, "gated_act"), _stream()))
+    return out
+
+
+def stream_cast(x: torch.Tensor, out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = x in ``out``'s number format; ``x``: float32, same shape."""
+    _want(x, "stream_cast x", torch.float32)
+    _want(out, "stream_cast out")
+    if out.shape != x.shape:
+        raise KernelError(f"stream_cast: x {tuple(x.shape)}, out {tuple(out.shape)}")
+    lib = library("elementwise")
+    _check(lib, lib.lp_stream_cast(x.data_ptr(), out.data_ptr(), _code(out, "stream_cast out"), x.numel(),
+                                   *_clear_args(clear, "stream_cast"), _stream()))
+    return out
 
 
 def stream_add(x: torch.Tensor, other: Optional[torch.Tensor] = None, vector: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -1469,6 +1576,50 @@ def expert_scale(hidden: torch.Tensor, weights: torch.Tensor, expert_size: int, 
     lib = library("routing")
     _check(lib, lib.lp_expert_scale(hidden.data_ptr(), _code(hidden, "expert_scale hidden"), hidden.shape[1],
                                     weights.data_ptr(), E, T, E, int(expert_size), *_clear_args(clear, "expert_scale"), _stream()))
+    return hidden
+
+
+def route_top(logits: torch.Tensor, bias: Optional[torch.Tensor], weights: torch.Tensor, *, num_experts: int, top: int) -> torch.Tensor:
+    """weights[t, e] for the E = ``num_experts`` experts: the ``top`` largest of logits[t, e] + bias[e] are chosen and
+    weighted by the softmax over the chosen logits alone (zero elsewhere). Columns of ``logits`` beyond E are gates of
+    experts that every token uses: weights[t, E + i] = sigmoid(logits[t, E + i]). ``logits``: float32 [T, E + extra]
+    (may be a column slice); ``weights``: float32, same shape."""
+    zp, ldz = _slice(logits, "route_top logits")
+    _want(weights, "route_top weights", torch.float32, 2)
+    E = int(num_experts)
+    if weights.shape != logits.shape or logits.shape[1] < E:
+        raise KernelError(f"route_top: logits {tuple(logits.shape)}, weights {tuple(weights.shape)}, {E} experts")
+    if bias is not None:
+        _want(bias, "route_top bias", torch.float32, 1)
+        if bias.numel() != E:
+            raise KernelError(f"route_top: a bias of {bias.numel()} values for {E} experts")
+    lib = library("routing")
+    _check(lib, lib.lp_route_top(zp, ldz, _ptr(bias), weights.data_ptr(), weights.shape[1], logits.shape[0], E, int(top),
+                                 logits.shape[1] - E, _stream()))
+    return weights
+
+
+def expert_act(z: torch.Tensor, weights: Optional[torch.Tensor], hidden: torch.Tensor, *, num_experts: int, expert_size: int,
+               limit: float, limit_rest: float = 0.0, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Hidden activations of clamped gated experts from the float32 sums ``z`` [T, 2 * total] of one stacked product
+    (all gate sums, then all up sums): with g = min(gate, limit), u = clamp(up, -limit, limit),
+    hidden[t, c] = g * sigmoid(1.702 g) * (u + 1) * weights[t, expert of c]. The first ``num_experts * expert_size``
+    columns belong to the routed experts; the rest to one more expert (weights[:, num_experts], ``limit_rest``)."""
+    zp, ldz = _slice(z, "expert_act z")
+    _want(hidden, "expert_act hidden", ndim=2)
+    T, total = hidden.shape
+    if z.shape != (T, 2 * total):
+        raise KernelError(f"expert_act: z {tuple(z.shape)}, hidden {tuple(hidden.shape)}")
+    ldw = 0
+    if weights is not None:
+        _want(weights, "expert_act weights", torch.float32, 2)
+        ldw = weights.shape[1]
+        if weights.shape[0] != T:
+            raise KernelError(f"expert_act: weights {tuple(weights.shape)} for {T} tokens")
+    lib = library("routing")
+    _check(lib, lib.lp_expert_act(zp, ldz, total, hidden.data_ptr(), _code(hidden, "expert_act hidden"), _ptr(weights), ldw,
+                                  T, int(num_experts), int(expert_size), float(limit), float(limit_rest),
+                                  *_clear_args(clear, "expert_act"), _stream()))
     return hidden
 
 

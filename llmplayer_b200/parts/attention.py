@@ -20,7 +20,7 @@ from ..errors import ConfigError
 from ..kernels import ops
 from .base import MIXERS, POSITIONS, Part, PendingNorm, Runtime
 from .linear import Linear
-from .specs import BIAS, MATRIX, AttentionSpec, TensorSpec
+from .specs import BIAS, GAIN, MATRIX, AttentionSpec, TensorSpec
 
 
 class Attention(Part):
@@ -34,8 +34,10 @@ class Attention(Part):
             raise ConfigError(f"attention window must be positive or absent, got {s.window}")
         if not s.shares_kv and (s.k is None or s.v is None):
             raise ConfigError("an attention layer that keeps its own cache needs key and value projections")
-        if s.general and s.shares_kv:
-            raise ConfigError("a layer with biases, unit-norm heads, capped scores, sinks or values of another size keeps its own cache")
+        if s.sink is not None and s.sink_value is not None:
+            raise ConfigError("a learned sink per head and a constant sink exclude each other")
+        if s.shares_kv and (s.k_bias is not None or s.v_bias is not None or s.k_norm is not None):
+            raise ConfigError("a layer that attends over another layer's keys and values has no key or value tensors")
         if s.softcap is not None and not s.softcap > 0:
             raise ConfigError(f"score cap must be positive or absent, got {s.softcap}")
         self.spec = spec
@@ -47,6 +49,9 @@ class Attention(Part):
         self.stored_dim = -(-max(s.head_dim, self.value_dim) // 16) * 16 if s.general else s.head_dim
         self.bias: Optional[torch.Tensor] = None
         self.sinks: Optional[torch.Tensor] = None
+        self.q_gain: Optional[torch.Tensor] = None
+        self.k_gain: Optional[torch.Tensor] = None
+        self.output_bias: Optional[torch.Tensor] = None     # float32 [hidden]: what the output projection adds
 
     @property
     def capture_safe(self) -> bool:
@@ -69,6 +74,11 @@ class Attention(Part):
                 specs[name] = TensorSpec((rows,), BIAS)
         if s.sink is not None:
             specs[s.sink] = TensorSpec((s.num_heads,), BIAS)
+        for name in (s.q_norm, s.k_norm):
+            if name is not None:
+                specs[name] = TensorSpec((s.head_dim,), GAIN)
+        if s.o_bias is not None:
+            specs[s.o_bias] = TensorSpec((s.hidden_size,), BIAS)
         return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
@@ -85,19 +95,25 @@ class Attention(Part):
         self.out = Linear([o], runtime)
         self.position.load(tensors, runtime)
         if any(b is not None for b in (s.q_bias, s.k_bias, s.v_bias)):
-            parts = [(s.q_bias, s.num_heads * s.head_dim), (s.k_bias, s.num_kv_heads * s.head_dim),
-                     (s.v_bias, s.num_kv_heads * self.value_dim)]
+            parts = [(s.q_bias, s.num_heads * s.head_dim)]
+            if not s.shares_kv:
+                parts += [(s.k_bias, s.num_kv_heads * s.head_dim), (s.v_bias, s.num_kv_heads * self.value_dim)]
             self.bias = torch.cat([tensors[n].to(torch.float32) if n is not None else torch.zeros(rows)
                                    for n, rows in parts]).to(runtime.device).contiguous()
         if s.sink is not None:
             self.sinks = runtime.gain(tensors[s.sink])
+        elif s.sink_value is not None:
+            self.sinks = torch.full((s.num_heads,), float(s.sink_value), dtype=torch.float32, device=runtime.device)
+        self.q_gain = runtime.gain(tensors[s.q_norm]) if s.q_norm is not None else None
+        self.k_gain = runtime.gain(tensors[s.k_norm]) if s.k_norm is not None else None
+        self.output_bias = runtime.gain(tensors[s.o_bias]) if s.o_bias is not None else None
 
     # ------------------------------------------------------------------ cache
     def cache_request(self):
         s = self.spec
         if s.shares_kv:
             return None
-        return KVRequest(s.num_kv_heads, self.stored_dim, s.window)
+        return KVRequest(s.num_kv_heads, self.stored_dim, s.window if s.cache_window == "own" else s.cache_window)
 
     # ------------------------------------------------------------------ step
     def buffer_to_clear(self, ctx, tokens: int):
@@ -128,10 +144,12 @@ class Attention(Part):
         with ops.section("attention.out"):
             self.out.few(o, residual, ops.ACCUMULATE, zero=sums[:ops.FEW_TOKENS + T * F])
 
-    def _forward_general(self, ctx, cache, x, residual: torch.Tensor, then_norm=None, overwrite: bool = False) -> bool:
-        """A layer with biases, unit-norm heads, capped scores, sinks or values of another size than its keys:
-        projection with float32 sums, one kernel that adds the biases, rotates, norms and stores queries, keys and
-        values (heads padded to ``stored_dim``), then the attention kernels with the cap and the sinks as arguments."""
+    def _forward_general(self, ctx, cache, x, residual: torch.Tensor, then_norm=None, overwrite: bool = False,
+                         bias_later: bool = False) -> bool:
+        """A layer with biases, normed heads, capped scores, sinks or values of another size than its keys:
+        projection with float32 sums, one kernel that adds the biases, norms, rotates and stores queries, keys and
+        values (heads padded to ``stored_dim``), then the attention kernels with the cap and the sinks as arguments.
+        A layer that attends over another run's keys and values projects and prepares queries only."""
         s, rt = self.spec, self.runtime
         if isinstance(x, PendingNorm):
             x = x.tensor()
@@ -150,7 +168,8 @@ class Attention(Part):
             clear = residual if overwrite and residual.dtype == torch.float32 and self.out.needs_zero(T) else None
             ops.qkv_prepare(qkv, self.bias, rotation, ctx.positions, ctx.seq_ids, table, q, cache.pages, num_heads=H,
                             num_kv_heads=G, key_dim=s.head_dim, value_dim=self.value_dim, unit_norm_eps=s.unit_norm_eps,
-                            clear=clear)
+                            clear=clear, q_gain=self.q_gain, k_gain=self.k_gain, gain_eps=s.qk_norm_eps,
+                            write_kv=not s.shares_kv)
         o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
         with ops.section("attention.scores"):
             ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd, scale=s.scale,
@@ -160,17 +179,24 @@ class Attention(Part):
                 if clear is not None:
                     ctx.note_cleared()
                 self.out.store(o, residual, ctx)
+                if self.output_bias is not None and not bias_later:
+                    ops.stream_add(residual, None, self.output_bias)
                 return False
+            if self.output_bias is not None:
+                ops.stream_add(residual, None, self.output_bias)
+                then_norm = None            # the norm must see the bias as well
             return self.out.accumulate(o, residual, ctx, then_norm)
 
-    def forward(self, ctx, cache, x, residual: torch.Tensor, then_norm=None, overwrite: bool = False) -> bool:
+    def forward(self, ctx, cache, x, residual: torch.Tensor, then_norm=None, overwrite: bool = False,
+                bias_later: bool = False) -> bool:
         """Adds the layer's output into ``residual`` (``overwrite``: stores it there instead); returns whether
-        ``then_norm`` was fused. ``x``: the normed stream, or a :class:`PendingNorm` of it."""
+        ``then_norm`` was fused. ``x``: the normed stream, or a :class:`PendingNorm` of it. ``bias_later`` (with
+        ``overwrite``): the caller adds ``output_bias`` itself, in the kernel that reads the result."""
         s, rt = self.spec, self.runtime
         if cache is None:
             raise ConfigError("attention needs a key/value cache (its own or another run's)")
         if s.general:
-            return self._forward_general(ctx, cache, x, residual, then_norm, overwrite)
+            return self._forward_general(ctx, cache, x, residual, then_norm, overwrite, bias_later)
         if overwrite:
             residual.zero_()
         H, G, hd = s.num_heads, s.num_kv_heads, s.head_dim

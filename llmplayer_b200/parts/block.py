@@ -17,7 +17,7 @@ from ..kernels import ops
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, FollowingNorm, Part, PendingNorm, Runtime
 from ..errors import ConfigError
 from .linear import Linear
-from .specs import BIAS, MATRIX, BlockSpec, ParallelBlockSpec, SandwichBlockSpec, TensorSpec
+from .specs import BIAS, GAIN, MATRIX, BlockSpec, ParallelBlockSpec, PostNormBlockSpec, SandwichBlockSpec, TensorSpec
 
 
 class PreNormBlock(Part):
@@ -329,6 +329,118 @@ class SandwichBlock(Part):
         return add_normed(self.post_ffn_norm, follower.mixer_norm if follower else None, follower.mixer if follower else None)
 
 
+class PostNormBlock(Part):
+    """x += scale_m * norm_m(mixer(x)); x += scale_f * norm_f(ffn(x)): the sublayers read the stream itself, and each
+    result is RMS-normed (and multiplied by a per-feature layer scale, if the layer has one) before it is added.
+
+    A sublayer stores its result in a float32 buffer; ONE kernel then adds the additive vector of the sublayer's last
+    map (if the sublayer left it to the block: ``bias_later``), norms, scales, adds into the stream and writes the new
+    stream in the number format of the next sublayer's products (bfloat16 models; a float32 model's sublayers read the
+    stream in place). A sublayer with ``reads_stream`` (one that blends neighbouring tokens in float32, say) is handed
+    the float32 stream as it is. The feed-forward may be absent."""
+
+    def __init__(self, spec: PostNormBlockSpec):
+        self.spec = spec
+        if (spec.ffn is None) != (spec.post_ffn_norm is None) or (spec.ffn is None and spec.ffn_scale is not None):
+            raise ConfigError("a feed-forward comes with the norm behind it, or not at all")
+        self.mixer = MIXERS.build(spec.mixer)
+        self.post_mixer_norm = NORMS.build(spec.post_mixer_norm)
+        self.ffn = FEED_FORWARDS.build(spec.ffn) if spec.ffn is not None else None
+        self.post_ffn_norm = NORMS.build(spec.post_ffn_norm) if spec.ffn is not None else None
+        for norm in (self.post_mixer_norm, self.post_ffn_norm):
+            if norm is not None and not getattr(norm, "fusable_rms", False):
+                raise ConfigError("the norms of a post-norm block are RMS norms")
+        self.mixer_scale: Optional[torch.Tensor] = None
+        self.ffn_scale: Optional[torch.Tensor] = None
+        self._mixer_args = inspect.signature(self.mixer.forward).parameters
+        self._ffn_args = inspect.signature(self.ffn.forward).parameters if self.ffn is not None else {}
+
+    def children(self):
+        return tuple(p for p in (self.mixer, self.post_mixer_norm, self.ffn, self.post_ffn_norm) if p is not None)
+
+    @property
+    def capture_safe(self) -> bool:
+        return all(bool(getattr(part, "capture_safe", False)) for part in self.children())
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        out: Dict[str, TensorSpec] = {}
+        for part in self.children():
+            out.update(part.tensor_specs())
+        d = self.spec.post_mixer_norm.size
+        for name in (self.spec.mixer_scale, self.spec.ffn_scale):
+            if name is not None:
+                out[name] = TensorSpec((d,), GAIN)
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        for part in self.children():
+            part.load(tensors, runtime)
+        s = self.spec
+        self.mixer_scale = runtime.gain(tensors[s.mixer_scale]) if s.mixer_scale is not None else None
+        self.ffn_scale = runtime.gain(tensors[s.ffn_scale]) if s.ffn_scale is not None else None
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    kind_postnorm = True
+
+    def wants_cast(self) -> bool:
+        """Whether this block's first sublayer reads the stream in the products' number format (a copy that the
+        kernel in front of it can write) rather than the float32 stream itself."""
+        return self.runtime.act_dtype != torch.float32 and not getattr(self.mixer, "reads_stream", False)
+
+    def _run(self, part, args, ctx, cache, source, y) -> Optional[torch.Tensor]:
+        """Run a sublayer into ``y``; returns the additive vector it left to the block, if any."""
+        kwargs = {}
+        if "overwrite" in args:
+            kwargs["overwrite"] = True
+        else:
+            y.zero_()
+        later = "bias_later" in args and "overwrite" in args and getattr(part, "output_bias", None) is not None
+        if later:
+            kwargs["bias_later"] = True
+        if cache is _NO_CACHE:
+            part.forward(ctx, source, y, **kwargs)
+        else:
+            part.forward(ctx, cache, source, y, **kwargs)
+        return part.output_bias if later else None
+
+    def forward(self, ctx, cache, residual: torch.Tensor, normed_ready: bool = False, next_block=None) -> bool:
+        """Run the layer on the residual stream in place. ``normed_ready``: the previous block already left the
+        stream in the products' number format in the shared buffer. ``next_block``: the block that runs next; if it is
+        of this kind and wants such a copy, the kernel that adds this layer's last result writes it. Returns whether
+        it did."""
+        act = self.runtime.act_dtype
+        same = act == torch.float32                        # sublayers then read the stream in place
+        h = residual if same else ctx.buffer("stream_copy", tuple(residual.shape), act)
+        y = ctx.buffer("sublayer_out", tuple(residual.shape), torch.float32)
+        if self.wants_cast() and not normed_ready:
+            with ops.section("norm"):
+                ops.stream_cast(residual, h)
+        follower = next_block if getattr(next_block, "kind_postnorm", False) and not same else None
+        to_follower = follower is not None and follower.wants_cast()
+
+        def add_normed(post, scale, bias, copy: bool) -> bool:
+            with ops.section("norm"):
+                ops.post_norm_add(y, post.weight, post.spec.eps, residual, next_out=h if copy else None, y_bias=bias,
+                                  scale=scale)
+            return copy
+
+        reads_stream = getattr(self.mixer, "reads_stream", False)
+        bias = self._run(self.mixer, self._mixer_args, ctx, cache, residual if reads_stream else h, y)
+        if self.ffn is None:
+            return add_normed(self.post_mixer_norm, self.mixer_scale, bias, to_follower)
+        ffn_reads_stream = getattr(self.ffn, "reads_stream", False)
+        add_normed(self.post_mixer_norm, self.mixer_scale, bias, not same and not ffn_reads_stream)
+        bias = self._run(self.ffn, self._ffn_args, ctx, _NO_CACHE, residual if ffn_reads_stream else h, y)
+        return add_normed(self.post_ffn_norm, self.ffn_scale, bias, to_follower)
+
+
+_NO_CACHE = object()
+
+
+BLOCKS.register("postnorm", PostNormBlock)
 BLOCKS.register("sandwich", SandwichBlock)
 BLOCKS.register("prenorm", PreNormBlock)
 BLOCKS.register("parallel", ParallelBlock)

@@ -15,7 +15,7 @@ import torch
 from ..errors import ConfigError
 from .base import FEED_FORWARDS, Part, PendingNorm, Runtime
 from .linear import Linear
-from .specs import BIAS, MATRIX, MixtureSpec, SquaredReLUSpec, SwiGLUSpec, TensorSpec, XIELUSpec
+from .specs import BIAS, MATRIX, GatedDenseSpec, MixtureSpec, SquaredReLUSpec, SwiGLUSpec, TensorSpec, XIELUSpec
 
 
 class SwiGLU(Part):
@@ -64,6 +64,77 @@ class SwiGLU(Part):
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)
+
+
+class GatedDense(Part):
+    """down(act(gate x + b_g) * (up x + b_u)) + b_d with the tanh form of GELU (or silu) as the activation. Gate and up
+    are one stacked product with float32 sums; the additive vectors and the activation are applied to those sums in
+    float32 by one kernel. ``output_bias`` is what the down projection adds: a block that norms the result may add it
+    in the kernel that reads the result (``bias_later``)."""
+    capture_safe = True
+
+    def __init__(self, spec: GatedDenseSpec):
+        if spec.activation not in ("gelu_tanh", "silu"):
+            raise ConfigError(f"unknown activation {spec.activation!r} of a gated feed-forward")
+        if spec.intermediate_size <= 0:
+            raise ConfigError(f"a feed-forward of {spec.intermediate_size} hidden values")
+        self.spec = spec
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+        self.bias: Optional[torch.Tensor] = None
+        self.output_bias: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        s = self.spec
+        out = {s.gate: TensorSpec((s.intermediate_size, s.hidden_size), MATRIX),
+               s.up: TensorSpec((s.intermediate_size, s.hidden_size), MATRIX),
+               s.down: TensorSpec((s.hidden_size, s.intermediate_size), MATRIX)}
+        for name, size in ((s.gate_bias, s.intermediate_size), (s.up_bias, s.intermediate_size), (s.down_bias, s.hidden_size)):
+            if name is not None:
+                out[name] = TensorSpec((size,), BIAS)
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        s = self.spec
+        self.gate_up = Linear([tensors[s.gate], tensors[s.up]], runtime)       # rows: gate, then up
+        self.down = Linear([tensors[s.down]], runtime)
+        if s.gate_bias is not None or s.up_bias is not None:
+            self.bias = torch.cat([tensors[n].to(torch.float32) if n is not None else torch.zeros(s.intermediate_size)
+                                   for n in (s.gate_bias, s.up_bias)]).to(runtime.device).contiguous()
+        self.output_bias = runtime.gain(tensors[s.down_bias]) if s.down_bias is not None else None
+
+    def buffer_to_clear(self, ctx, tokens: int):
+        from ..kernels import ops
+        return self.gate_up.sums_into(ctx, tokens, "ffn_up", ops.STORE)
+
+    def forward(self, ctx, x, residual: torch.Tensor, overwrite: bool = False, bias_later: bool = False) -> bool:
+        """Adds the feed-forward's output into ``residual`` (``overwrite``: stores it there instead; with
+        ``bias_later`` the caller then adds ``output_bias`` itself)."""
+        from ..kernels import ops
+        if isinstance(x, PendingNorm):
+            x = x.tensor()
+        T, F = x.shape[0], self.spec.intermediate_size
+        z = ctx.buffer("ffn_up", (T, 2 * F), torch.float32)
+        with ops.section("ffn.gate_up"):
+            self.gate_up.store(x, z, ctx)
+        h = ctx.buffer("ffn_hidden", (T, F), self.runtime.act_dtype)
+        with ops.section("ffn.act"):
+            clear = residual if overwrite and residual.dtype == torch.float32 and self.down.needs_zero(T) else None
+            ops.gated_act(z, self.bias, h, self.spec.activation, clear=clear)
+        with ops.section("ffn.down"):
+            if clear is not None:
+                ctx.note_cleared()
+            if overwrite:
+                self.down.store(h, residual, ctx)
+            else:
+                self.down.accumulate(h, residual, ctx)
+            if self.output_bias is not None and not (overwrite and bias_later):
+                ops.stream_add(residual, None, self.output_bias)
+        return False
+
+
+FEED_FORWARDS.register("gated_dense", GatedDense)
 
 
 class XIELUFeedForward(Part):
@@ -201,6 +272,20 @@ class Mixture(Part):
 
     def __init__(self, spec: MixtureSpec):
         s, r = spec, spec.routing
+        if r.scoring not in ("sigmoid_groups", "softmax_top"):
+            raise ConfigError(f"unknown scoring {r.scoring!r} of a router")
+        if s.activation not in ("silu", "clamped"):
+            raise ConfigError(f"unknown activation {s.activation!r} of the experts")
+        if s.activation == "clamped" and (not s.limit > 0 or (s.shared_size > 0 and not s.shared_limit > 0)):
+            raise ConfigError(f"clamped experts need positive limits, got {s.limit} and {s.shared_limit}")
+        if r.scoring == "softmax_top" and (r.groups != 1 or r.keep_groups != 1):
+            raise ConfigError("a router that takes the largest logits has no groups")
+        if r.router_bias is not None and r.scoring != "softmax_top":
+            raise ConfigError("only a router that takes the largest logits adds a bias to them")
+        if s.activation == "clamped" and s.shared_size > 0 and s.shared_gate is None:
+            raise ConfigError("the shared expert of clamped experts comes with its gate")
+        if s.shared_gate is not None and (s.shared_size <= 0 or r.scoring != "softmax_top" or s.activation != "clamped"):
+            raise ConfigError("a gate of the shared expert belongs to clamped experts chosen by their largest logits")
         if r.num_experts <= 0 or r.groups <= 0 or r.num_experts % r.groups:
             raise ConfigError(f"{r.num_experts} experts cannot form {r.groups} equal groups")
         if not 0 < r.keep_groups <= r.groups:
@@ -229,6 +314,10 @@ class Mixture(Part):
             out[prefix + "up"] = TensorSpec((size, s.hidden_size), MATRIX)
             out[prefix + "down"] = TensorSpec((s.hidden_size, size), MATRIX)
         out[s.routing.router] = TensorSpec((s.routing.num_experts, s.hidden_size), MATRIX)
+        if s.routing.router_bias is not None:
+            out[s.routing.router_bias] = TensorSpec((s.routing.num_experts,), BIAS)
+        if s.shared_gate is not None:
+            out[s.shared_gate] = TensorSpec((1, s.hidden_size), MATRIX)
         return out
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
@@ -239,8 +328,12 @@ class Mixture(Part):
         up = torch.cat([tensors[p + "up"] for p, _ in experts], dim=0)
         down = torch.cat([tensors[p + "down"] for p, _ in experts], dim=1).contiguous()
         self.total = gate.shape[0]
-        self.router = Linear([tensors[s.routing.router]], runtime)
-        self.gate_up = Linear([gate, up], runtime, gated=True)
+        # the shared expert's gate is one more row of the router's product
+        self.router = Linear([tensors[s.routing.router]] + ([tensors[s.shared_gate]] if s.shared_gate is not None else []),
+                             runtime)
+        self.router_bias = runtime.gain(tensors[s.routing.router_bias]) if s.routing.router_bias is not None else None
+        # silu experts: the gated product applies the activation itself; clamped ones: float32 sums, then a kernel
+        self.gate_up = Linear([gate, up], runtime, gated=s.activation == "silu")
         self.down = Linear([down], runtime)
 
     def buffer_to_clear(self, ctx, tokens: int):
@@ -254,17 +347,29 @@ class Mixture(Part):
         if isinstance(x, PendingNorm):
             x = x.tensor()
         T = x.shape[0]
-        logits = ctx.buffer("router_logits", (T, r.num_experts), torch.float32)
+        columns = self.router.out_features              # the experts' logits (and the shared expert's gate)
+        logits = ctx.buffer("router_logits", (T, columns), torch.float32)
         with ops.section("ffn.router"):
             self.router.store(x, logits, ctx)
-            weights = ctx.buffer("router_weights", (T, r.num_experts), torch.float32)
-            ops.route(logits, weights, groups=r.groups, keep=r.keep_groups, top=r.top)
+            weights = ctx.buffer("router_weights", (T, columns), torch.float32)
+            if r.scoring == "softmax_top":
+                ops.route_top(logits, self.router_bias, weights, num_experts=r.num_experts, top=r.top)
+            else:
+                ops.route(logits, weights, groups=r.groups, keep=r.keep_groups, top=r.top)
         h = ctx.buffer("ffn_hidden", (T, self.total), self.runtime.act_dtype)
-        with ops.section("ffn.gate_up"):
-            self.gate_up.swiglu(x, h, ctx)
-        with ops.section("ffn.weights"):
-            clear = residual if overwrite and residual.dtype == torch.float32 and self.down.needs_zero(T) else None
-            ops.expert_scale(h, weights, s.expert_size, clear=clear)
+        clear = residual if overwrite and residual.dtype == torch.float32 and self.down.needs_zero(T) else None
+        if s.activation == "clamped":
+            z = ctx.buffer("ffn_up", (T, 2 * self.total), torch.float32)
+            with ops.section("ffn.gate_up"):
+                self.gate_up.store(x, z, ctx)
+            with ops.section("ffn.weights"):
+                ops.expert_act(z, weights, h, num_experts=r.num_experts, expert_size=s.expert_size, limit=s.limit,
+                               limit_rest=s.shared_limit, clear=clear)
+        else:
+            with ops.section("ffn.gate_up"):
+                self.gate_up.swiglu(x, h, ctx)
+            with ops.section("ffn.weights"):
+                ops.expert_scale(h, weights, s.expert_size, clear=clear)
         with ops.section("ffn.down"):
             if clear is not None:
                 ctx.note_cleared()

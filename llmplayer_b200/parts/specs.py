@@ -106,11 +106,20 @@ class AttentionSpec:
     softcap: Optional[float] = None      # score <- softcap * tanh(score / softcap), after the scale
     sink: Optional[str] = None           # tensor [heads]: a learned logit per head in the softmax's denominator, without key or value
     exact_weights: bool = False          # softmax weights meet the values at float32 precision also on the tensor cores
+    q_norm: Optional[str] = None         # gains [head_dim], shared by the heads: BEFORE the rotation every query / key head is
+    k_norm: Optional[str] = None         # RMS-normed over head_dim with that gain and ``qk_norm_eps`` inside the root
+    qk_norm_eps: float = 0.0
+    o_bias: Optional[str] = None         # additive vector [hidden] of the output projection
+    sink_value: Optional[float] = None   # a constant logit (the same for every head) in the softmax's denominator: 0.0 adds one to it
+    # The window that the layer's cache must keep (None: everything) when layers that attend over this layer's keys look
+    # further back than the layer itself; "own": the layer's own ``window``.
+    cache_window: object = "own"
 
     @property
     def general(self) -> bool:
         return (self.value_dim not in (None, self.head_dim) or any(b is not None for b in (self.q_bias, self.k_bias, self.v_bias))
-                or self.unit_norm_eps is not None or self.softcap is not None or self.sink is not None or self.exact_weights)
+                or self.unit_norm_eps is not None or self.softcap is not None or self.sink is not None or self.exact_weights
+                or self.q_norm is not None or self.k_norm is not None or self.o_bias is not None or self.sink_value is not None)
 
 
 @dataclass(frozen=True)
@@ -211,6 +220,55 @@ class MatrixMemorySpec:
 
 
 @dataclass(frozen=True)
+class TimeMixSpec:
+    """Time mixing with a matrix state per head and a decay per key channel that depends on the token (the WKV
+    recurrence of the RWKV family, version 6). With x' the previous token's input (zeros before a sequence's first
+    token), each of r, k, v, g, w reads its own blend x + (x' - x) * mu_s (``mu`` + "r", "k", "v", "g", "w"; [hidden]
+    each). r, k, v = ``r`` / ``k`` / ``v`` of their blends ([heads * head_dim, hidden]); the output gate is
+    silu(``gate`` blend_g); the decay is exp(-exp(``decay_up`` tanh(``decay_down`` blend_w) + ``decay_bias``)) per head
+    and key channel (the width of the factor is read off ``decay_down``). Per head, with the bonus ``bonus``
+    [heads, head_dim]:
+
+        o_t = (S_(t-1) + diag(bonus) k_t v_t^T)^T r_t;    S_t = diag(decay_t) S_(t-1) + k_t v_t^T
+
+    Each head's o_t is divided by its root mean square (``norm_eps`` inside the root), the heads are multiplied by the
+    gain ``out_norm`` [heads * head_dim] and by the gate, and projected by ``o``. The state (S and the previous token's
+    input) is float32 and starts at zero."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    norm_eps: float
+    mu: str
+    r: str
+    k: str
+    v: str
+    gate: str
+    decay_down: str
+    decay_up: str
+    decay_bias: str
+    bonus: str
+    out_norm: str
+    o: str
+    kind: str = "time_mix"
+
+
+@dataclass(frozen=True)
+class GatedDenseSpec:
+    """Dense gated feed-forward down(act(gate x + b_g) * (up x + b_u)) + b_d with ``activation`` "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))) or "silu"; the additive vectors are optional."""
+    hidden_size: int
+    intermediate_size: int
+    gate: str
+    up: str
+    down: str
+    gate_bias: Optional[str] = None
+    up_bias: Optional[str] = None
+    down_bias: Optional[str] = None
+    activation: str = "gelu_tanh"
+    kind: str = "gated_dense"
+
+
+@dataclass(frozen=True)
 class SquaredReLUSpec:
     """Dense feed-forward down(relu(up x)^2)."""
     hidden_size: int
@@ -224,19 +282,29 @@ class SquaredReLUSpec:
 class ExpertRoutingSpec:
     """How a token chooses its experts: scores sigmoid(router x); the experts form ``groups`` equal groups of
     neighbours whose score is the sum of their two largest scores; only experts of the ``keep_groups`` best groups
-    may be chosen; the ``top`` largest scores among those win, and their weights are the scores divided by their sum."""
+    may be chosen; the ``top`` largest scores among those win, and their weights are the scores divided by their sum.
+
+    ``scoring="softmax_top"``: the ``top`` experts with the largest logits router x + ``router_bias`` are chosen, and
+    their weights are the softmax over the chosen logits alone (``groups`` and ``keep_groups`` stay 1)."""
     num_experts: int
     top: int
     groups: int
     keep_groups: int
     router: str
+    scoring: str = "sigmoid_groups"
+    router_bias: Optional[str] = None
 
 
 @dataclass(frozen=True)
 class MixtureSpec:
     """Mixture of gated experts down(silu(gate x) * (up x)) without biases. Expert e's tensors are
     ``expert_prefix`` + ``e<e>.`` + gate / up / down. ``shared_size`` > 0: one more expert of that size
-    (``shared_prefix`` + gate / up / down) runs for every token with weight one."""
+    (``shared_prefix`` + gate / up / down) runs for every token with weight one.
+
+    ``activation="clamped"``: an expert is down(g * sigmoid(1.702 g) * (u + 1)) with g = min(gate x, limit) and
+    u = clamp(up x, -limit, limit); ``limit`` belongs to the routed experts, ``shared_limit`` to the shared one.
+    ``shared_gate``: a matrix [1, hidden]; the shared expert's output is multiplied by sigmoid(shared_gate x), one
+    number per token."""
     hidden_size: int
     expert_size: int
     routing: ExpertRoutingSpec
@@ -244,6 +312,10 @@ class MixtureSpec:
     shared_size: int = 0
     shared_prefix: Optional[str] = None
     kind: str = "mixture"
+    activation: str = "silu"
+    limit: float = 0.0
+    shared_limit: float = 0.0
+    shared_gate: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -300,6 +372,21 @@ class SandwichBlockSpec:
     ffn: Optional[object] = None
     post_ffn_norm: Optional[NormSpec] = None
     kind: str = "sandwich"
+
+
+@dataclass(frozen=True)
+class PostNormBlockSpec:
+    """One layer whose sublayers read the stream itself and whose results are normed before they are added:
+    x += mixer_scale * post_mixer_norm(mixer(x)); x += ffn_scale * post_ffn_norm(ffn(x)). The scales (tensors [hidden],
+    optional) multiply the normed result element by element (a layer scale). ``ffn`` may be None (then its norm and
+    scale are None as well)."""
+    mixer: object
+    post_mixer_norm: NormSpec
+    mixer_scale: Optional[str] = None
+    ffn: Optional[object] = None
+    post_ffn_norm: Optional[NormSpec] = None
+    ffn_scale: Optional[str] = None
+    kind: str = "postnorm"
 
 
 @dataclass(frozen=True)
