@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--shape 1b|3b|8b]
     python bench.py --design ramupel [--size s|m|l] [--layers N]      (the hybrid design beside Llama at equal size)
     python bench.py --design botuvik [--size s|m|l] [--layers N]      (the same for the Botuvik design, beside both)
+    python bench.py --design zasitar [--size s|m|l] [--layers N]      (the Zasitar design beside Botuvik and Llama)
 
 One "step" is one decode step of the whole batch. The default run has the Llama-3.2-1B shape, a batch of 8
 sequences with 512-token prompts in a cache sized for a context of 4096. Every figure comes from the library's
@@ -27,6 +28,9 @@ the same width, depth, head count and feed-forward parameters, both with random 
 section of the model walk of each and what the mixers' core kernels reach of their rooflines.
 ``--design botuvik`` does the same for the Botuvik design (matrix-memory layers, capped attention with sinks, dense
 and routed feed-forwards) beside Ramupel, the closest existing design (a recurrence among attention layers), and Llama.
+``--design zasitar`` does the same for the Zasitar design (time-mixing layers, sliding-window attention with normed
+heads and keys shared between layers, results normed behind the sublayers) beside Botuvik, the closest existing design
+(a matrix recurrence among attention layers with sinks, dense and routed feed-forwards), and Llama.
 """
 from __future__ import annotations
 
@@ -188,6 +192,33 @@ def botuvik_config(size, layers):
             "layers": [dict(memory if i % 4 == 0 else attention, mlp=routed if i % 2 else dense) for i in range(layers)]}
 
 
+ZASITAR_WINDOW = 1024          # half of the measured prompt: the window's edge passes through the prompt kernels' tiles
+
+
+def zasitar_config(size, layers):
+    """Every fourth layer time mixing (heads of 64 channels over the whole width), the others attention over a window
+    of ZASITAR_WINDOW tokens (grouped as in the Llama beside it, rotation over half of each head); of every four
+    layers the third attends over the second's keys and values; dense and routed feed-forwards alternate as in the
+    Botuvik beside it (8 experts of a quarter of the dense width, 2 chosen, plus a gated shared expert of that size)."""
+    width, heads, _, _, ff = HYBRID_SIZES[size]
+    hd = width // heads
+    mixer = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+             "mask": {"size": ZASITAR_WINDOW},
+             "rot": {"base": 500000.0, "dims": hd // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    time_mix = {"type": "wkv", "mixer": {"heads": width // 64, "dim": 64}}
+    dense = {"kind": "dense", "ff": ff}
+    routed = {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0}, "shared": {"ff": ff // 4, "limit": 7.0},
+              "router": {"experts": 8, "top": 2}}
+    out = []
+    for i in range(layers):
+        if i % 4 == 0:
+            layer = dict(time_mix)
+        else:
+            layer = {"type": "attention", "mixer": dict(mixer, kv_from=i - 1) if i % 4 == 2 else dict(mixer)}
+        out.append(dict(layer, mlp=routed if i % 2 else dense))
+    return {"architecture": "Zasitar", "vocab": 32000, "width": width, "norm": {"eps": 1e-5}, "layers": out}
+
+
 def compare_designs(args, peaks) -> int:
     import torch
     from llmplayer_b200 import Engine
@@ -203,9 +234,10 @@ def compare_designs(args, peaks) -> int:
     gen = torch.Generator().manual_seed(5)
     clocks = ClockSampler()
     clocks.start()
-    botuvik = args.design == "botuvik"
-    out = {"metric": f"prefill and decode tok/s of the {'Botuvik' if botuvik else 'Ramupel'} design beside "
-                     f"{'Ramupel and ' if botuvik else ''}Llama at equal size (bf16)", "impl": "ours",
+    botuvik, zasitar = args.design == "botuvik", args.design == "zasitar"
+    title = {"botuvik": "Botuvik design beside Ramupel and ", "zasitar": "Zasitar design beside Botuvik and ",
+             "ramupel": "Ramupel design beside "}[args.design]
+    out = {"metric": f"prefill and decode tok/s of the {title}Llama at equal size (bf16)", "impl": "ours",
            "layers": layers, "batch": batch, "prompt_len": prompt, "prefill_len": prefill_len, "peaks": peaks, "sizes": {}}
     try:
         for size in ([args.size] if args.size else sorted(HYBRID_SIZES, key="sml".index)):
@@ -213,6 +245,8 @@ def compare_designs(args, peaks) -> int:
             designs = list(zip(("ramupel", "llama"), hybrid_configs(size, layers)))
             if botuvik:
                 designs.insert(0, ("botuvik", botuvik_config(size, layers)))
+            if zasitar:
+                designs = [("zasitar", zasitar_config(size, layers)), ("botuvik", botuvik_config(size, layers)), designs[1]]
             for name, raw in designs:
                 vocab = raw.get("vocab", raw.get("vocab_size"))
                 tmp = tempfile.mkdtemp(prefix="llmplayer_b200_bench_")
@@ -273,9 +307,11 @@ def compare_designs(args, peaks) -> int:
                 }
                 del engine, profiled
                 torch.cuda.empty_cache()
-            row["rooflines"] = hybrid_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len)
-            if botuvik:
+            row["rooflines"] = {} if zasitar else hybrid_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len)
+            if botuvik or zasitar:
                 row["rooflines"].update(botuvik_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len))
+            if zasitar:
+                row["rooflines"].update(zasitar_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len))
             out["sizes"][size] = row
         print(json.dumps(out))
         return 0
@@ -342,6 +378,50 @@ def botuvik_rooflines(size, layers, row, peaks, batch, context, n):
     }
 
 
+def zasitar_rooflines(size, layers, row, peaks, batch, context, n):
+    """The Zasitar kernels beside their Botuvik twins (``botuvik_rooflines``): prompt kernels against the bf16 tensor
+    peak, decode and elementwise kernels against the copy bandwidth. A windowed layer's work counts the keys inside
+    the window only."""
+    width, heads, _, _, ff = HYBRID_SIZES[size]
+    n_mix = sum(1 for i in range(layers) if i % 4 == 0)
+    n_att = layers - n_mix
+    n_routed = sum(1 for i in range(layers) if i % 2)
+    flops, gbs = peaks["bf16_tflops"] * 1e12, peaks["hbm_gbs"] * 1e9
+    z = row["zasitar"]
+    hd, G, W = width // heads, max(1, heads // 4), ZASITAR_WINDOW
+    th, tn = width // 64, 64
+
+    def frac(work, ms, count, peak):
+        return None if not ms or not count else work / (ms / count / 1e3) / peak
+    seen = sum(min(i + 1, W) for i in range(n))                  # (query, key) pairs inside the window
+    routed_rows = 8 * (ff // 4) + ff // 4
+    pre, dec = z["prefill_sections_ms"], z["decode_sections_ms"]
+    out = {
+        "prefill zasitar attention, keys in the window (of tensor peak)": frac(heads * seen * 4 * hd, pre.get("attention.scores"), n_att, flops),
+        "prefill zasitar recurrence (of tensor peak)": frac(6.0 * th * tn * tn * n, pre.get("recurrence.scan"), n_mix, flops),
+        "prefill zasitar routed gate/up product, all experts (of tensor peak)": frac(
+            2.0 * n * width * 2 * routed_rows, pre.get("ffn.gate_up"), n_routed, flops),
+        "decode zasitar attention (of copy bandwidth)": frac(
+            batch * min(context, W) * 2 * G * hd * 2, dec.get("attention.scores"), n_att, gbs),
+        "decode zasitar recurrence (of copy bandwidth)": frac(batch * th * tn * tn * 4 * 2, dec.get("recurrence.scan"), n_mix, gbs),
+        # the kernel behind every sublayer: reads the sublayer's float32 result and the float32 stream, writes the
+        # stream and its bfloat16 copy (two per layer that has a feed-forward)
+        "prefill zasitar norm behind a sublayer (of copy bandwidth)": frac(n * width * (4 + 4 + 4 + 2), pre.get("norm"), 2 * layers, gbs),
+        # blends of neighbouring tokens: reads the stream, writes five bfloat16 blends
+        "prefill zasitar token blends (of copy bandwidth)": frac(n * width * (4 + 5 * 2), pre.get("recurrence.shift"), n_mix, gbs),
+    }
+    b, l = row.get("botuvik"), row.get("llama")
+    if b is not None:
+        out["prefill botuvik norm behind a sublayer (of copy bandwidth)"] = frac(
+            n * width * (4 + 4 + 4 + 2), b["prefill_sections_ms"].get("norm"), 2 * layers, gbs)
+    if l is not None:
+        out["prefill llama attention (of tensor peak)"] = frac(
+            heads * n * (n + 1) * 2 * hd, l["prefill_sections_ms"].get("attention.scores"), layers, flops)
+        out["decode llama attention (of copy bandwidth)"] = frac(
+            batch * context * 2 * G * hd * 2, l["decode_sections_ms"].get("attention.scores"), layers, gbs)
+    return out
+
+
 def spread(values):
     return {"median": statistics.median(values), "min": min(values), "max": max(values), "repeats": len(values)}
 
@@ -362,10 +442,10 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true",
                     help="measure only the 2,048-token prefill (small runs for profiling)")
     ap.add_argument("--profile", action="store_true", help="add the device time per section of the model walk")
-    ap.add_argument("--design", default="llama", choices=("llama", "ramupel", "botuvik"),
-                    help="ramupel / botuvik: that design beside the closest others at equal size (another workload; see "
+    ap.add_argument("--design", default="llama", choices=("llama", "ramupel", "botuvik", "zasitar"),
+                    help="ramupel / botuvik / zasitar: that design beside the closest others at equal size (another workload; see "
                          "the module text)")
-    ap.add_argument("--size", default=None, choices=sorted(HYBRID_SIZES), help="with --design ramupel / botuvik: one size only")
+    ap.add_argument("--size", default=None, choices=sorted(HYBRID_SIZES), help="with --design ramupel / botuvik / zasitar: one size only")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -376,7 +456,7 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU library")
         return 2
-    if args.design in ("ramupel", "botuvik"):
+    if args.design in ("ramupel", "botuvik", "zasitar"):
         return compare_designs(args, load_peaks())
     args.warmup = max(3, args.warmup)
     repeats = max(1, args.repeats)

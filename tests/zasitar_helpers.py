@@ -1,0 +1,173 @@
+"""Small Zasitar configurations with sizes of their own, and seeded model folders for them."""
+import json
+import os
+
+import torch
+
+# Odd sizes: values wider than keys (heads are stored padded), rotation over part of a head without stretching, a
+# layer that attends over layer 0's keys through a WIDER window than layer 0's own (the cache must keep the wider one),
+# time mixing whose heads do not fill the width, a decay factor of 5, a layer without a feed-forward, no shared
+# expert in one mixture, a window wider than every prompt of the tests.
+SMALL = {
+    "architecture": "Zasitar", "vocab": 211, "width": 72, "norm": {"eps": 2e-6},
+    "layers": [
+        {"type": "attention",
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 40, "scale": 0.5, "mask": {"size": 9},
+                   "rot": {"base": 10000.0, "dims": 16}},
+         "mlp": {"kind": "moe", "expert": {"ff": 24, "limit": 1.5}, "shared": {"ff": 40, "limit": 0.75},
+                 "router": {"experts": 6, "top": 2}}},
+        {"type": "wkv", "mixer": {"heads": 3, "dim": 20}, "mlp": {"kind": "dense", "ff": 104}},
+        {"type": "attention",
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 40, "scale": 0.3, "mask": {"size": 17}, "kv_from": 0,
+                   "rot": {"base": 10000.0, "dims": 16}},
+         "mlp": None},
+        {"type": "wkv", "mixer": {"heads": 1, "dim": 36},
+         "mlp": {"kind": "moe", "expert": {"ff": 16, "limit": 3.0}, "shared": None, "router": {"experts": 4, "top": 1}}},
+        {"type": "attention",
+         "mixer": {"heads": 3, "kv_heads": 3, "dim": 16, "vdim": 16, "scale": 0.7, "mask": {"size": 1000},
+                   "rot": {"base": 300.0, "dims": 16,
+                           "scaling": {"factor": 3.0, "low": 2.0, "high": 6.0, "original": 96}}},
+         "mlp": {"kind": "dense", "ff": 56}},
+    ],
+}
+# Sizes the tensor-core kernels take (heads of 64 and 128, keys wider than values): a window of 70 (its edge crosses
+# a page's border of 64 while decoding), eight query heads on one key head, a window of exactly two pages, a shared
+# layer with a NARROWER window than the layer whose keys it reads, frequencies that the stretching divides, blends and
+# leaves alone, three of eight experts.
+WIDE = {
+    "architecture": "Zasitar", "vocab": 384, "width": 128, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "wkv", "mixer": {"heads": 2, "dim": 64}, "mlp": {"kind": "dense", "ff": 256}},
+        {"type": "attention",
+         "mixer": {"heads": 8, "kv_heads": 1, "dim": 64, "vdim": 64, "scale": 0.2, "mask": {"size": 70},
+                   "rot": {"base": 1000000.0, "dims": 32,
+                           "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}}},
+         "mlp": {"kind": "moe", "expert": {"ff": 64, "limit": 2.0}, "shared": {"ff": 128, "limit": 4.0},
+                 "router": {"experts": 8, "top": 3}}},
+        {"type": "attention",
+         "mixer": {"heads": 2, "kv_heads": 2, "dim": 128, "vdim": 64, "scale": 0.09, "mask": {"size": 128},
+                   "rot": {"base": 10000.0, "dims": 128}},
+         "mlp": {"kind": "dense", "ff": 128}},
+        {"type": "attention",
+         "mixer": {"heads": 8, "kv_heads": 1, "dim": 64, "vdim": 64, "scale": 0.15, "mask": {"size": 33}, "kv_from": 1,
+                   "rot": {"base": 1000000.0, "dims": 32,
+                           "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}}},
+         "mlp": {"kind": "dense", "ff": 128}},
+    ],
+}
+# A width that is no multiple of 8 (every product leaves the tensor cores, also in bfloat16), a window of ONE token
+# (a token sees itself and the sink), every expert chosen (top = experts), one expert of two, a rotation over two
+# features only, five query heads on one key head.
+RAGGED = {
+    "architecture": "Zasitar", "vocab": 131, "width": 52, "norm": {"eps": 3e-5},
+    "layers": [
+        {"type": "wkv", "mixer": {"heads": 2, "dim": 6},
+         "mlp": {"kind": "moe", "expert": {"ff": 12, "limit": 0.5}, "shared": {"ff": 20, "limit": 1.25},
+                 "router": {"experts": 3, "top": 3}}},
+        {"type": "attention",
+         "mixer": {"heads": 5, "kv_heads": 1, "dim": 10, "vdim": 12, "scale": 0.4, "mask": {"size": 1},
+                   "rot": {"base": 100.0, "dims": 2}},
+         "mlp": {"kind": "dense", "ff": 60}},
+        {"type": "attention",
+         "mixer": {"heads": 2, "kv_heads": 2, "dim": 12, "vdim": 6, "scale": 0.6, "mask": {"size": 64},
+                   "rot": {"base": 50.0, "dims": 12, "scaling": {"factor": 2.0, "low": 0.5, "high": 3.0, "original": 40}}},
+         "mlp": {"kind": "moe", "expert": {"ff": 8, "limit": 2.5}, "shared": None, "router": {"experts": 2, "top": 1}}},
+    ],
+}
+CONFIGS = {"small": (SMALL, 31, 0.09), "wide": (WIDE, 32, 0.06), "ragged": (RAGGED, 33, 0.1)}
+
+# bfloat16: at most four times the worst error that the comparisons of each configuration achieved on a B200 at all
+# but one position in fifty (see test_zasitar_model.close)
+BFLOAT16_BOUND = {"small": 6e-2, "wide": 4e-2, "ragged": 6e-2}
+ROUTE_CHANNELS = 8          # channels of the stream that carry each token's routing code (see make_model)
+
+
+def bound(dtype, name):
+    return 2e-5 if dtype == "float32" else BFLOAT16_BOUND[name]
+
+
+def make_model(tmp_path, name, dtype="bfloat16"):
+    """A model folder for configuration ``name``: the library's seeded writer, then
+
+    * the tensors whose random draw around zero would switch a mechanism off are drawn again: the additive vectors of
+      the projections and of the routers, the blends' weights (between 0 and 1, so that the previous token takes
+      part), the decay's bias (decays from nearly 1 to nearly 0), the bonus, the layer scales;
+    * the routing is made robust against rounding: the first ROUTE_CHANNELS channels of the stream carry a code per
+      token (distinct levels with wide gaps, in the embedding), nothing else writes to these channels (the layer scales
+      are zero there), and every router reads only them, one channel per expert. The stream is read as it is, so an
+      expert's logit is the token's code plus the router's additive vector: no choice of experts rests on a close call,
+      and bfloat16 runs choose as float64 does;
+    * time mixing divides each head's output by its own root mean square, so early in a sequence, where the state holds
+      little, the output's SIGN is that of r . (u * k) of the token itself: with unrelated random maps that product is
+      near zero every so often and the output then rests on rounding. The maps of r are therefore drawn as the maps of
+      k plus a third of a random matrix, with a positive bonus.
+    """
+    from llmplayer_b200.config import config_from_dict
+    from llmplayer_b200.weights import write_random_model
+    from llmplayer_b200.weights.safetensors_io import write_safetensors
+    from plain_llama import read_safetensors
+    raw, seed, std = CONFIGS[name]
+    out = os.path.join(str(tmp_path), f"zasitar_{name}_{dtype}")
+    write_random_model(config_from_dict(raw), seed, out, dtype=dtype, std=std)
+    path = os.path.join(out, "model.safetensors")
+    tensors = read_safetensors(path)
+    gen = torch.Generator().manual_seed(seed + 100)
+    store = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    d, C = raw["width"], ROUTE_CHANNELS
+
+    def draw(*shape, scale=1.0, shift=0.0):
+        return (shift + scale * torch.randn(*shape, generator=gen)).to(store)
+
+    # a token's code: a permutation of levels whose values, and whose sums with the routers' vectors below, stay apart
+    levels = torch.tensor([-1.88, -1.55, -1.22, -0.35, 0.01, 0.62, 1.3, 1.95])
+    embed = tensors["embed"].to(torch.float32)
+    for t in range(raw["vocab"]):
+        embed[t, :C] = levels[torch.randperm(C, generator=gen)]
+    tensors["embed"] = embed.to(store)
+    for i, layer in enumerate(raw["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        scales = ["ls1"]
+        if layer["type"] == "attention":
+            tensors[p + "mix.q.b"] = draw(m["heads"] * m["dim"], scale=0.3)
+            tensors[p + "mix.o.b"] = draw(d, scale=0.3)
+            if "kv_from" not in m:
+                tensors[p + "mix.k.b"] = draw(m["kv_heads"] * m["dim"], scale=0.3)
+                tensors[p + "mix.v.b"] = draw(m["kv_heads"] * m["vdim"], scale=0.3)
+        else:
+            for b in "rkvgw":
+                tensors[p + "mix.mu." + b] = torch.rand(d, generator=gen).to(store)
+            tensors[p + "mix.w0"] = draw(m["heads"] * m["dim"], scale=1.5, shift=-2.0)
+            tensors[p + "mix.u"] = (0.5 + torch.rand(m["heads"], m["dim"], generator=gen)).to(store)
+            tensors[p + "mix.r"] = (tensors[p + "mix.k"].to(torch.float32) + 0.3 * tensors[p + "mix.r"].to(torch.float32)).to(store)
+            tensors[p + "mix.w1"] = draw(*tensors[p + "mix.w1"].shape, scale=0.3)
+            tensors[p + "mix.w2"] = draw(*tensors[p + "mix.w2"].shape, scale=0.3)
+        mlp = layer["mlp"]
+        if mlp is not None:
+            scales.append("ls2")
+        if mlp is not None and mlp["kind"] == "dense":
+            for n, rows in (("gate", mlp["ff"]), ("up", mlp["ff"]), ("down", d)):
+                tensors[f"{p}mlp.{n}.b"] = draw(rows, scale=0.3)
+        elif mlp is not None:
+            E = mlp["router"]["experts"]
+            assert E <= C
+            router = torch.zeros(E, d)
+            router[torch.arange(E), torch.arange(E)] = 1.0
+            tensors[p + "mlp.router"] = router.to(store)
+            # multiples of 1/8: sums with the levels stay at least 0.03 apart and are exact in bfloat16
+            tensors[p + "mlp.router.b"] = (torch.randint(-4, 5, (E,), generator=gen).float() / 8.0).to(store)
+            if mlp.get("shared"):
+                tensors[p + "mlp.shared.sg"] = draw(1, d, scale=0.4)
+        for n in scales:
+            scale = (0.6 + 0.8 * torch.rand(d, generator=gen))
+            scale[:C] = 0
+            tensors[p + n] = scale.to(store)
+    write_safetensors(path, tensors, metadata={"format": "pt"})
+    with open(os.path.join(out, "config.json"), "w") as fh:
+        json.dump(raw, fh, indent=1)
+    return out
+
+
+def plain_logits(model_dir, tokens, rows=None, gaps=None):
+    import plain_zasitar
+    cfg, w = plain_zasitar.read_model(model_dir)
+    return plain_zasitar.forward(cfg, w, tokens, dtype=torch.float64, rows=rows, gaps=gaps)
