@@ -285,9 +285,11 @@ exp_gates_kernel(const float* __restrict__ proj, int ld, int i_off, int f_off, c
 template <typename TOut>
 __global__ void __launch_bounds__(256)
 token_shift_kernel(const float* __restrict__ x, float* __restrict__ last, const float* __restrict__ mu, const int* __restrict__ slots,
-                   const int* __restrict__ q_start, const int* __restrict__ seq_ids, TOut* __restrict__ out, int T, int d, int S) {
+                   const int* __restrict__ q_start, const int* __restrict__ seq_ids, TOut* __restrict__ out, int T, int d, int S,
+                   float* __restrict__ zero, long long zero_count) {
     lp_grid_release();
     lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
     const int t = blockIdx.x;
     const int b = seq_ids[t];
     const int t0 = q_start[b], t1 = q_start[b + 1];
@@ -448,11 +450,12 @@ extern "C" int lp_exp_gates(const float* proj, int ld, int i_off, int f_off, con
 
 // x: float32 [T, d]; last: float32 [slots, d]; mu: float32 [S, d]; out: [S, T, d] float32 or bfloat16.
 extern "C" int lp_token_shift(const float* x, float* last, const float* mu, const int* slots, const int* q_start,
-                              const int* seq_ids, void* out, int out_dtype, int T, int d, int S, cudaStream_t stream) {
+                              const int* seq_ids, void* out, int out_dtype, int T, int d, int S, float* zero, long long zero_count,
+                              cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d <= 0 || S <= 0) LP_REFUSE("token_shift: rows of %d values, %d blends", d, S);
-    if (out_dtype == LP_F32) lp_launch(token_shift_kernel<float>, T, 256, 0, stream, x, last, mu, slots, q_start, seq_ids, (float*)out, T, d, S);
-    else if (out_dtype == LP_BF16) lp_launch(token_shift_kernel<__nv_bfloat16>, T, 256, 0, stream, x, last, mu, slots, q_start, seq_ids, (__nv_bfloat16*)out, T, d, S);
+    if (out_dtype == LP_F32) lp_launch(token_shift_kernel<float>, T, 256, 0, stream, x, last, mu, slots, q_start, seq_ids, (float*)out, T, d, S, zero, zero_count);
+    else if (out_dtype == LP_BF16) lp_launch(token_shift_kernel<__nv_bfloat16>, T, 256, 0, stream, x, last, mu, slots, q_start, seq_ids, (__nv_bfloat16*)out, T, d, S, zero, zero_count);
     else LP_REFUSE("token_shift: output dtype code %d", out_dtype);
     return lp_check_launch("token_shift");
 }

@@ -184,6 +184,41 @@ expert_act_kernel(const float* __restrict__ z, int ldz, int total, TH* __restric
     }
 }
 
+// The same, four columns of one expert per thread and a token per blockIdx.y (expert sizes, row lengths and strides of a
+// multiple of four values, bfloat16 out): two float4 loads, one 8-byte store.
+__global__ void __launch_bounds__(256)
+expert_act_vec4_kernel(const float* __restrict__ z, int ldz, int total, __nv_bfloat16* __restrict__ hidden,
+                       const float* __restrict__ weights, int ldw, int E, int ff, float limit, float limit_rest,
+                       float* __restrict__ zero, long long zero_count) {
+    lp_grid_release();
+    lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
+    const long long t = blockIdx.y;
+    const float* row = z + t * ldz;
+    const int quads = total / 4;
+    for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += gridDim.x * blockDim.x) {
+        const int c = q * 4;
+        const int e = c < E * ff ? c / ff : E;
+        const float lim = e < E ? limit : limit_rest;
+        const float w = weights ? weights[t * ldw + e] : 1.0f;
+        const float4 g4 = *reinterpret_cast<const float4*>(row + c);
+        const float4 u4 = *reinterpret_cast<const float4*>(row + total + c);
+        const float gs[4] = {g4.x, g4.y, g4.z, g4.w}, us[4] = {u4.x, u4.y, u4.z, u4.w};
+        float v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float g = fminf(gs[k], lim);
+            const float u = fminf(fmaxf(us[k], -lim), lim);
+            v[k] = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+            if (weights) v[k] *= w;
+        }
+        uint2 packed;
+        *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(v[0], v[1]);
+        *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(hidden + t * total + c) = packed;
+    }
+}
+
 }  // namespace
 
 // z: float32 [T, ldz] (E logits per row); weights: float32 [T, ldw], E values per row written.
@@ -244,6 +279,14 @@ extern "C" int lp_expert_act(const float* z, int ldz, int total, void* hidden, i
     if (ldz < 2 * total) LP_REFUSE("expert_act: rows of %d values for 2 x %d sums", ldz, total);
     if (weights && ldw < E + (total > E * ff ? 1 : 0)) LP_REFUSE("expert_act: rows of %d weights", ldw);
     const long long n = (long long)T * total;
+    if (dtype == LP_BF16 && total % 4 == 0 && ff % 4 == 0 && ldz % 4 == 0 && T <= 65535 &&
+        (reinterpret_cast<uintptr_t>(z) & 15) == 0 && (reinterpret_cast<uintptr_t>(hidden) & 7) == 0) {
+        int bx = (total / 4 + 255) / 256;
+        if (bx > 32) bx = 32;
+        lp_launch(expert_act_vec4_kernel, dim3(bx, T), 256, 0, stream, z, ldz, total, (__nv_bfloat16*)hidden, weights, ldw, E, ff,
+                  limit, limit_rest, zero, zero_count);
+        return lp_check_launch("expert_act");
+    }
     long long blocks = (n + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == LP_F32) lp_launch(expert_act_kernel<float>, (unsigned)blocks, 256, 0, stream, z, ldz, total, (float*)hidden, weights, ldw, T, E, ff, limit, limit_rest, zero, zero_count);

@@ -84,7 +84,7 @@ _SIGNATURES = {
     "linear_attention": {
         "lp_gla_decay": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _F, _I, _P],
         "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _I, _P, _P],
-        "lp_token_shift": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "lp_token_shift": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "lp_gla_finish": [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _I, _I, _I, _P, _P],
         "lp_exp_gates": [_P, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _P],
     },
@@ -1381,10 +1381,10 @@ def exp_gates(proj: torch.Tensor, i_off: int, f_off: int, bias_i: Optional[torch
 
 
 def token_shift(x: torch.Tensor, last: torch.Tensor, mu: torch.Tensor, slots: torch.Tensor, q_start: torch.Tensor,
-                seq_ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+                seq_ids: torch.Tensor, out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[s, t] = x[t] + (x[t - 1] - x[t]) * mu[s] for the S rows of ``mu`` (float32 [S, d]); the token before a
     sequence's first new token is the row of its slot in ``last`` (float32 [slots, d]), which then receives the
-    sequence's last new token. ``x``: float32 [T, d]; ``out``: [S, T, d]."""
+    sequence's last new token. ``x``: float32 [T, d]; ``out``: [S, T, d]. ``clear``: a float32 buffer zeroed on the side."""
     _want(x, "token_shift x", torch.float32, 2)
     _want(last, "token_shift last", torch.float32, 2)
     _want(mu, "token_shift mu", torch.float32, 2)
@@ -1398,7 +1398,8 @@ def token_shift(x: torch.Tensor, last: torch.Tensor, mu: torch.Tensor, slots: to
         raise KernelError(f"token_shift: x {tuple(x.shape)}, last {tuple(last.shape)}, mu {tuple(mu.shape)}, out {tuple(out.shape)}")
     lib = library("linear_attention")
     _check(lib, lib.lp_token_shift(x.data_ptr(), last.data_ptr(), mu.data_ptr(), slots.data_ptr(), q_start.data_ptr(),
-                                   seq_ids.data_ptr(), out.data_ptr(), _code(out, "token_shift out"), T, d, S, _stream()))
+                                   seq_ids.data_ptr(), out.data_ptr(), _code(out, "token_shift out"), T, d, S,
+                                   *_clear_args(clear, "token_shift"), _stream()))
     return out
 
 

@@ -421,20 +421,25 @@ class PostNormBlock(Part):
         follower = next_block if getattr(next_block, "kind_postnorm", False) and not same else None
         to_follower = follower is not None and follower.wants_cast()
 
-        def add_normed(post, scale, bias, copy: bool) -> bool:
+        def add_normed(post, scale, bias, copy: bool, consumer) -> bool:
+            # the part that runs next may want the buffer of its first product zero: cleared here on the side
+            clear = PreNormBlock._clear_for(ctx, consumer, residual.shape[0]) if consumer is not None else None
             with ops.section("norm"):
                 ops.post_norm_add(y, post.weight, post.spec.eps, residual, next_out=h if copy else None, y_bias=bias,
-                                  scale=scale)
+                                  scale=scale, clear=clear)
+            if clear is not None:
+                ctx.note_cleared()
             return copy
 
         reads_stream = getattr(self.mixer, "reads_stream", False)
         bias = self._run(self.mixer, self._mixer_args, ctx, cache, residual if reads_stream else h, y)
+        after = follower.mixer if follower is not None else None
         if self.ffn is None:
-            return add_normed(self.post_mixer_norm, self.mixer_scale, bias, to_follower)
+            return add_normed(self.post_mixer_norm, self.mixer_scale, bias, to_follower, after)
         ffn_reads_stream = getattr(self.ffn, "reads_stream", False)
-        add_normed(self.post_mixer_norm, self.mixer_scale, bias, not same and not ffn_reads_stream)
+        add_normed(self.post_mixer_norm, self.mixer_scale, bias, not same and not ffn_reads_stream, self.ffn)
         bias = self._run(self.ffn, self._ffn_args, ctx, _NO_CACHE, residual if ffn_reads_stream else h, y)
-        return add_normed(self.post_ffn_norm, self.ffn_scale, bias, to_follower)
+        return add_normed(self.post_ffn_norm, self.ffn_scale, bias, to_follower, after)
 
 
 _NO_CACHE = object()

@@ -102,17 +102,22 @@ class TimeMix(Part):
         C = H * n
         state, last = cache.blocks
         blends = ctx.buffer("time_mix_blends", (len(BLENDS), T, d), rt.act_dtype)
-        with ops.section("recurrence.shift"):
-            ops.token_shift(x, last, self.mu, ctx.slots, ctx.q_start, ctx.seq_ids, blends)
         # the five maps write side by side into one float32 buffer: r | k | v | gate | decay factor (slices start
-        # at multiples of 8 values)
+        # at multiples of 8 values). Maps that sum partial results want their slice zero: the blends' kernel clears
+        # the whole buffer on the side
         width = -(-C // 8) * 8
         ld = 4 * width + -(-self.decay_rank // 8) * 8
         proj = ctx.buffer("mixer_proj", (T, ld), torch.float32)
+        cleared = any(self.maps[b].needs_zero(T) for b in BLENDS)
+        with ops.section("recurrence.shift"):
+            ops.token_shift(x, last, self.mu, ctx.slots, ctx.q_start, ctx.seq_ids, blends, clear=proj if cleared else None)
         with ops.section("recurrence.proj"):
             for i, b in enumerate(BLENDS):
                 m = self.maps[b]
+                if cleared:
+                    ctx.note_cleared()
                 m.store(blends[i], proj[:, i * width:i * width + m.out_features], ctx)
+            ctx.take_cleared()
         decay = ctx.buffer("gla_decay", (T, C), torch.float32)
         with ops.section("recurrence.decay"):
             ops.gla_decay(proj[:, 4 * width:4 * width + self.decay_rank], self.decay_up, self.decay_bias, decay,

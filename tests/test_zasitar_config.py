@@ -6,7 +6,7 @@ import math
 import pytest
 import torch
 
-from zasitar_helpers import CONFIGS, RAGGED, SMALL, WIDE
+from zasitar_helpers import CONFIGS, MIXED, RAGGED, SMALL, WIDE
 
 
 def cfg_of(raw):
@@ -63,6 +63,7 @@ def test_order_of_runs_and_whose_cache_they_read():
     runs = cfg_of(WIDE).layout().run_order()
     assert [r.reads_cache_of for r in runs] == [None, None, None, 1]
     assert not any(r.reads_cache_of for r in cfg_of(RAGGED).layout().run_order())
+    assert [r.reads_cache_of for r in cfg_of(MIXED).layout().run_order()] == [None, None, 1, 1, None, None, None]
 
 
 def test_tensors_and_cache_requests():
@@ -94,6 +95,8 @@ def test_tensors_and_cache_requests():
     assert reqs[3][0].shape == (1, 36, 36) and reqs[4] == KVRequest(3, 16, 1000)
     wide = Model(cfg_of(WIDE).layout()).cache_requests()
     assert wide[1] == KVRequest(1, 64, 70) and wide[3] is None and wide[2] == KVRequest(2, 128, 128)
+    mixed = Model(cfg_of(MIXED).layout()).cache_requests()
+    assert mixed[1] == KVRequest(2, 32, 300) and mixed[2] is None and mixed[3] is None and mixed[5] == KVRequest(1, 80, 64)
 
 
 def test_stretched_frequencies():

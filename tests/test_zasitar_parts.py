@@ -79,7 +79,8 @@ def test_gated_tanh_gelu(T, F):
     assert float((erf - ref).abs().max()) > 20 * float((exact.double().cpu() - ref).abs().max())
 
 
-@pytest.mark.parametrize("E,ff,rest,limit,limit_rest", [(6, 24, 40, 1.5, 0.75), (4, 16, 0, 3.0, 0.0), (3, 12, 20, 0.5, 1.25), (1, 8, 8, 1.0, 2.0)])
+@pytest.mark.parametrize("E,ff,rest,limit,limit_rest", [(6, 24, 40, 1.5, 0.75), (4, 16, 0, 3.0, 0.0), (3, 12, 20, 0.5, 1.25), (1, 8, 8, 1.0, 2.0),
+                                                        (2, 6, 10, 2.5, 1.0)])
 def test_clamped_expert_activation(E, ff, rest, limit, limit_rest):
     """Sums well beyond the limits: min on the gate only from above, the up sum from both sides, (u + 1), and the
     constant 1.702; the last columns belong to an expert with a limit and a weight column of its own."""

@@ -74,11 +74,44 @@ RAGGED = {
          "mlp": {"kind": "moe", "expert": {"ff": 8, "limit": 2.5}, "shared": None, "router": {"experts": 2, "top": 1}}},
     ],
 }
-CONFIGS = {"small": (SMALL, 31, 0.09), "wide": (WIDE, 32, 0.06), "ragged": (RAGGED, 33, 0.1)}
+# Another order and other sizes again: time mixing first and once more without a feed-forward behind it, TWO layers
+# that read the same layer's keys (one through a window of 300 over keys whose own layer sees 5, one with experts
+# behind it), three query heads per key head, a rotation over the whole head, keys of 80 with values of 48, one head
+# of 256, five of eight experts with and without a shared one, time-mixing heads of 32 and 48.
+MIXED = {
+    "architecture": "Zasitar", "vocab": 300, "width": 96, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "wkv", "mixer": {"heads": 3, "dim": 32},
+         "mlp": {"kind": "moe", "expert": {"ff": 16, "limit": 1.0}, "shared": {"ff": 32, "limit": 2.0},
+                 "router": {"experts": 8, "top": 5}}},
+        {"type": "attention",
+         "mixer": {"heads": 6, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.25, "mask": {"size": 5},
+                   "rot": {"base": 5000.0, "dims": 32}},
+         "mlp": {"kind": "dense", "ff": 160}},
+        {"type": "attention",
+         "mixer": {"heads": 6, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.12, "mask": {"size": 300}, "kv_from": 1,
+                   "rot": {"base": 5000.0, "dims": 32}},
+         "mlp": None},
+        {"type": "attention",
+         "mixer": {"heads": 6, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.3, "mask": {"size": 5}, "kv_from": 1,
+                   "rot": {"base": 5000.0, "dims": 32}},
+         "mlp": {"kind": "moe", "expert": {"ff": 24, "limit": 6.0}, "shared": None, "router": {"experts": 8, "top": 5}}},
+        {"type": "wkv", "mixer": {"heads": 2, "dim": 48}, "mlp": None},
+        {"type": "attention",
+         "mixer": {"heads": 2, "kv_heads": 1, "dim": 80, "vdim": 48, "scale": 0.11, "mask": {"size": 64},
+                   "rot": {"base": 20000.0, "dims": 40, "scaling": {"factor": 2.5, "low": 1.0, "high": 8.0, "original": 128}}},
+         "mlp": {"kind": "dense", "ff": 200}},
+        {"type": "attention",
+         "mixer": {"heads": 1, "kv_heads": 1, "dim": 256, "vdim": 256, "scale": 0.0625, "mask": {"size": 100},
+                   "rot": {"base": 1000.0, "dims": 64}},
+         "mlp": {"kind": "dense", "ff": 64}},
+    ],
+}
+CONFIGS = {"small": (SMALL, 31, 0.09), "wide": (WIDE, 32, 0.06), "ragged": (RAGGED, 33, 0.1), "mixed": (MIXED, 34, 0.07)}
 
 # bfloat16: at most four times the worst error that the comparisons of each configuration achieved on a B200 at all
-# but one position in fifty (see test_zasitar_model.close)
-BFLOAT16_BOUND = {"small": 6e-2, "wide": 4e-2, "ragged": 6e-2}
+# but one position in fifty (8.1e-3, 6.9e-3, 8.0e-3, 7.5e-3; see test_zasitar_model.close)
+BFLOAT16_BOUND = {"small": 3e-2, "wide": 2.7e-2, "ragged": 3e-2, "mixed": 2.9e-2}
 ROUTE_CHANNELS = 8          # channels of the stream that carry each token's routing code (see make_model)
 
 
