@@ -306,6 +306,45 @@ token_shift_kernel(const float* __restrict__ x, float* __restrict__ last, const 
     }
 }
 
+// The same, four neighbouring features per thread (rows of a multiple of four values): float4 loads, and for bfloat16
+// blends one 8-byte store per blend.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+token_shift_vec4_kernel(const float* __restrict__ x, float* __restrict__ last, const float* __restrict__ mu, const int* __restrict__ slots,
+                        const int* __restrict__ q_start, const int* __restrict__ seq_ids, TOut* __restrict__ out, int T, int d, int S,
+                        float* __restrict__ zero, long long zero_count) {
+    lp_grid_release();
+    lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
+    const int t = blockIdx.x;
+    const int b = seq_ids[t];
+    const int t0 = q_start[b], t1 = q_start[b + 1];
+    const bool first = t == t0;
+    float* kept = last + (long long)slots[b] * d;
+    const float* cur = x + (long long)t * d;
+    const float* prev = first ? kept : cur - d;
+    const float* newest = x + (long long)(t1 - 1) * d;
+    for (int i = threadIdx.x * 4; i < d; i += blockDim.x * 4) {
+        const float4 c = *reinterpret_cast<const float4*>(cur + i);
+        const float4 p = *reinterpret_cast<const float4*>(prev + i);
+        if (first) *reinterpret_cast<float4*>(kept + i) = *reinterpret_cast<const float4*>(newest + i);
+        for (int s = 0; s < S; ++s) {
+            const float4 m = *reinterpret_cast<const float4*>(mu + (long long)s * d + i);
+            const float v0 = fmaf(p.x - c.x, m.x, c.x), v1 = fmaf(p.y - c.y, m.y, c.y);
+            const float v2 = fmaf(p.z - c.z, m.z, c.z), v3 = fmaf(p.w - c.w, m.w, c.w);
+            TOut* at = out + ((long long)s * T + t) * d + i;
+            if constexpr (sizeof(TOut) == 4) {
+                *reinterpret_cast<float4*>(at) = make_float4(v0, v1, v2, v3);
+            } else {
+                uint2 packed;
+                *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(v0, v1);
+                *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(v2, v3);
+                *reinterpret_cast<uint2*>(at) = packed;
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------- finish
 // out[t, h * dv + j] = o[t, h, j] / sqrt(mean_j o^2 + eps) * gain[j] * silu(gate[t, h * dv + j]); a warp per (t, h).
 // Variants: rows of o that are `xs` apart (xs > dv: further columns follow a head's values), a gain per head
@@ -454,6 +493,14 @@ extern "C" int lp_token_shift(const float* x, float* last, const float* mu, cons
                               cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d <= 0 || S <= 0) LP_REFUSE("token_shift: rows of %d values, %d blends", d, S);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(last) | reinterpret_cast<uintptr_t>(mu) |
+                           reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    if (d % 4 == 0 && aligned && (out_dtype == LP_F32 || out_dtype == LP_BF16)) {
+        const int threads = d >= 1024 ? 256 : d >= 512 ? 128 : 64;
+        if (out_dtype == LP_F32) lp_launch(token_shift_vec4_kernel<float>, T, threads, 0, stream, x, last, mu, slots, q_start, seq_ids, (float*)out, T, d, S, zero, zero_count);
+        else lp_launch(token_shift_vec4_kernel<__nv_bfloat16>, T, threads, 0, stream, x, last, mu, slots, q_start, seq_ids, (__nv_bfloat16*)out, T, d, S, zero, zero_count);
+        return lp_check_launch("token_shift");
+    }
     if (out_dtype == LP_F32) lp_launch(token_shift_kernel<float>, T, 256, 0, stream, x, last, mu, slots, q_start, seq_ids, (float*)out, T, d, S, zero, zero_count);
     else if (out_dtype == LP_BF16) lp_launch(token_shift_kernel<__nv_bfloat16>, T, 256, 0, stream, x, last, mu, slots, q_start, seq_ids, (__nv_bfloat16*)out, T, d, S, zero, zero_count);
     else LP_REFUSE("token_shift: output dtype code %d", out_dtype);

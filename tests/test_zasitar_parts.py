@@ -379,12 +379,13 @@ def run_time_mix_kernels(x, w, H, n, eps, state, last, slots, q_start, max_new):
     return out, blends, decay
 
 
-def test_blends_with_the_previous_token():
+@pytest.mark.parametrize("d", [52, 50, 1028, 2048])
+def test_blends_with_the_previous_token(d):
     """Two sequences in slots 3 and 1 of five over three steps: before a sequence's first token stands a row of
-    zeros, before the first token of a later step the last token of the step before; the other slots stay untouched."""
+    zeros, before the first token of a later step the last token of the step before; the other slots stay untouched.
+    Rows of a multiple of four values (four features per thread) and others; a buffer cleared on the side."""
     from llmplayer_b200.kernels import ops
     torch.manual_seed(11)
-    d = 52
     seqs = [torch.randn(9, d), torch.randn(5, d)]
     mu = torch.rand(5, d)
     last = torch.zeros(5, d, device="cuda")
@@ -393,7 +394,9 @@ def test_blends_with_the_previous_token():
     for a, b in [(4, 1), (1, 1), (4, 3)]:
         x = torch.cat([seqs[0][at[0]:at[0] + a], seqs[1][at[1]:at[1] + b]])
         out = torch.empty(5, a + b, d, device="cuda")
-        ops.token_shift(x.cuda(), last, mu.cuda(), i32([3, 1]), i32([0, a, a + b]), i32([0] * a + [1] * b), out)
+        side = torch.full((1000,), 3.0, device="cuda")
+        ops.token_shift(x.cuda(), last, mu.cuda(), i32([3, 1]), i32([0, a, a + b]), i32([0] * a + [1] * b), out, clear=side[:777])
+        assert float(side[:777].abs().max()) == 0.0 and float((side[777:] - 3.0).abs().max()) == 0.0
         for s, (seq, lo, cnt, off) in enumerate(((seqs[0], at[0], a, 0), (seqs[1], at[1], b, a))):
             full = torch.cat([torch.zeros(1, d), seq]).double()
             cur, prev = full[1 + lo:1 + lo + cnt], full[lo:lo + cnt]
