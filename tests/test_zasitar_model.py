@@ -15,7 +15,7 @@ from zasitar_helpers import CONFIGS, bound, make_model, plain_logits
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-NAMES = ["small", "wide", "ragged", "mixed"]
+NAMES = ["small", "wide", "ragged", "mixed", "recurrent", "attentive"]
 
 
 def close(got, ref, dtype, name, what):
@@ -49,7 +49,7 @@ def reference(model_dir, tokens):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name,length", [("small", 1), ("small", 2), ("small", 97), ("small", 300), ("wide", 33), ("wide", 71),
                                          ("wide", 200), ("wide", 321), ("ragged", 3), ("ragged", 270), ("mixed", 4),
-                                         ("mixed", 66), ("mixed", 310)])
+                                         ("mixed", 66), ("mixed", 310), ("recurrent", 280), ("attentive", 150)])
 def test_whole_sequence(tmp_path, name, length, dtype):
     from llmplayer_b200 import Engine
     model_dir = make_model(tmp_path, name, dtype)
