@@ -61,12 +61,14 @@ class PageMap:
     """Pages of one group of layers: which page holds which block of positions of which slot.
 
     ``window`` (in positions) lets the map give back pages that no later query
-    can reach; ``None`` keeps every page until the slot is released.
+    can reach; ``None`` keeps every page until the slot is released. ``keep_first``: the pages
+    that hold a sequence's first so many positions are never given back before that.
     """
 
-    def __init__(self, num_pages: int, window: Optional[int] = None, page_size: int = PAGE_SIZE):
+    def __init__(self, num_pages: int, window: Optional[int] = None, page_size: int = PAGE_SIZE, keep_first: int = 0):
         self.page_size = page_size
         self.window = window
+        self.keep_first = max(0, int(keep_first or 0))
         self.pool = FreeList(num_pages, "page")
         self._pages: Dict[int, List[int]] = {}     # slot -> page id per block of positions (-1: given back)
 
@@ -98,7 +100,8 @@ class PageMap:
             return
         first_needed = length - self.window + 1
         pages = self._pages[slot]
-        for block in range(min(len(pages), max(0, first_needed) // self.page_size)):
+        kept = -(-self.keep_first // self.page_size)          # blocks that hold the positions kept for good
+        for block in range(kept, min(len(pages), max(0, first_needed) // self.page_size)):
             if pages[block] >= 0:
                 self.pool.give_back(pages[block])
                 pages[block] = -1

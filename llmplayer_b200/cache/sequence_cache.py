@@ -27,10 +27,12 @@ from .pages import PAGE_SIZE, FreeList, PageMap
 
 @dataclass(frozen=True)
 class KVRequest:
-    """Keys and values of every position (or of a window of positions) of a sequence."""
+    """Keys and values of every position (or of a window of positions) of a sequence. ``keep_first``: with a window,
+    the pages that hold a sequence's first so many positions are kept as well."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -48,6 +50,20 @@ class StateRequest:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class BundleRequest:
+    """What a run keeps when its mixer is made of several mixers that each keep something: one request (a paged one, a
+    state block, a tuple of state blocks, or None) per member, in the members' order."""
+    members: Tuple[object, ...]
+
+
+class BundleView:
+    """The views of a :class:`BundleRequest`'s members, in order (None for a member that keeps nothing)."""
+
+    def __init__(self, members: Sequence[object]):
+        self.members = list(members)
+
+
 class KVGroup:
     """Storage of the runs that share one paged request.
 
@@ -59,7 +75,7 @@ class KVGroup:
     def __init__(self, request, runs: Sequence[int], num_pages: int, dtype: torch.dtype, device):
         self.request = request
         self.runs = list(runs)
-        self.pages = PageMap(num_pages, window=request.window)
+        self.pages = PageMap(num_pages, window=request.window, keep_first=getattr(request, "keep_first", 0))
         if isinstance(request, RowsRequest):
             page_shape = (PAGE_SIZE, request.width)
         else:
@@ -108,25 +124,46 @@ class SequenceCache:
         self._length: Dict[int, int] = {}
         self.groups: List[KVGroup] = []
         self._views: List[object] = [None] * len(requests)
-        by_request: Dict[object, List[int]] = {}
-        for run, req in enumerate(requests):
+        # every paged request (a run's own, or a member's of a run's bundle) is a leaf with a key of its own
+        leaves: List[Tuple[object, object]] = []
+
+        def paged_leaves(key, req):
             if isinstance(req, (KVRequest, RowsRequest)):
-                by_request.setdefault(req, []).append(run)
-        for req, runs in by_request.items():
-            group = KVGroup(req, runs, self.num_pages, kv_dtype, device)
-            for run in runs:
-                self._views[run] = KVView(len(self.groups), group.view_of(run))
+                leaves.append((key, req))
+            elif isinstance(req, BundleRequest):
+                for i, member in enumerate(req.members):
+                    paged_leaves(key + (i,), member)
+
+        for run, req in enumerate(requests):
+            paged_leaves((run,), req)
+        by_request: Dict[object, List[object]] = {}
+        for key, req in leaves:
+            by_request.setdefault(req, []).append(key)
+        paged_views: Dict[object, KVView] = {}
+        for req, keys in by_request.items():
+            group = KVGroup(req, keys, self.num_pages, kv_dtype, device)
+            for key in keys:
+                paged_views[key] = KVView(len(self.groups), group.view_of(key))
             self.groups.append(group)
         self._state_rows: List[torch.Tensor] = []
-        for run, req in enumerate(requests):
+
+        def make_view(key, req):
+            if req is None:
+                return None
+            if isinstance(req, (KVRequest, RowsRequest)):
+                return paged_views[key]
+            if isinstance(req, BundleRequest):
+                return BundleView([make_view(key + (i,), member) for i, member in enumerate(req.members)])
             if isinstance(req, StateRequest):
                 req = (req,)
             if isinstance(req, tuple) and req and all(isinstance(r, StateRequest) for r in req):
                 blocks = [torch.zeros((self.max_slots,) + tuple(r.shape), dtype=r.dtype, device=device) for r in req]
                 self._state_rows.extend(blocks)
-                self._views[run] = StateView(blocks[0], blocks)
-            elif req is not None and not isinstance(req, (KVRequest, RowsRequest)):
-                raise CacheError(f"run {run}: unknown cache request {req!r}")
+                return StateView(blocks[0], blocks)
+            raise CacheError(f"run {key[0]}: unknown cache request {req!r}")
+
+        for run, req in enumerate(requests):
+            self._views[run] = make_view((run,), req)
 
     # ------------------------------------------------------------------ slots
     def acquire(self) -> int:

@@ -147,6 +147,7 @@ struct ScoreExtras {
     float cap_log2;
     float scale_over_cap;
     const float* sinks;
+    int keep;          // with a window: a sequence's first `keep` tokens stay visible to every later query (prompt kernels)
 };
 // tanh from the hardware's exp2 and a fast division: absolute error of about 1e-7
 __device__ __forceinline__ float lp_tanh_exp2(float x) {

@@ -50,6 +50,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     const int first_pos = pos0 + row0, last_pos = pos0 + row0 + rows - 1;
     const int lo = window > 0 ? max(0, first_pos - window + 1) : 0;
     const int page_lo = lo / PAGE, page_hi = last_pos / PAGE;
+    // a window that keeps a sequence's first tokens visible: the pages that hold them (and lie before the window's
+    // pages) are visited first; page number of the v-th visited page:
+    const int keep = window > 0 ? extras.keep : 0;
+    const int kept_pages = min(page_lo, (min(keep, lo) + PAGE - 1) / PAGE);
+    const int visited = kept_pages + page_hi - page_lo + 1;
+    auto page_of = [&](int v) { return v < kept_pages ? v : page_lo + v - kept_pages; };
     const int* table = page_table + (size_t)b * pt_stride;
     const int stage_bytes = 2 * PAGE * hd * 2;
 
@@ -79,18 +85,19 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     for (int i = 0; i < KSTEPS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
 
-    load_page(smem, pages, table[page_lo], G, g, hd, tid, 128);
+    load_page(smem, pages, table[page_of(0)], G, g, hd, tid, 128);
     cp_async_commit();
-    for (int p = page_lo; p <= page_hi; ++p) {
-        const int cur = (p - page_lo) & 1;
-        if (p + 1 <= page_hi) load_page(smem + (cur ^ 1) * stage_bytes, pages, table[p + 1], G, g, hd, tid, 128);
+    for (int vp = 0; vp < visited; ++vp) {
+        const int p = page_of(vp);
+        const int cur = vp & 1;
+        if (vp + 1 < visited) load_page(smem + (cur ^ 1) * stage_bytes, pages, table[page_of(vp + 1)], G, g, hd, tid, 128);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
         const int key_base = p * PAGE;
         // pages wholly after this warp's rows, or wholly before their windows, contribute nothing
         const bool active = key_base <= warp_last_pos &&
-                            (window <= 0 || key_base + PAGE - 1 > warp_first_pos - window);
+                            (window <= 0 || key_base + PAGE - 1 > warp_first_pos - window || key_base < keep);
         if (active) {
             const uint32_t k_tile = smem_u32(smem + cur * stage_bytes);
             const uint32_t v_tile = k_tile + PAGE * hd * 2;
@@ -109,7 +116,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                     const int key = key_base + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = (e < 2) ? pos_lo : pos_hi;
                     float v = shaped_score(s[nt][e], scale_log2, extras);
-                    if (edge && (key > pos || (window > 0 && key <= pos - window))) v = NEG_BIG;
+                    if (edge && (key > pos || (window > 0 && key <= pos - window && key >= keep))) v = NEG_BIG;
                     s[nt][e] = v;
                     if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
                 }
@@ -197,6 +204,12 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
     const int first_pos = pos0 + row0, last_pos = pos0 + row0 + rows - 1;
     const int lo = window > 0 ? max(0, first_pos - window + 1) : 0;
     const int page_lo = lo / PAGE, page_hi = last_pos / PAGE;
+    // a window that keeps a sequence's first tokens visible: the pages that hold them (and lie before the window's
+    // pages) are visited first; page number of the v-th visited page:
+    const int keep = window > 0 ? extras.keep : 0;
+    const int kept_pages = min(page_lo, (min(keep, lo) + PAGE - 1) / PAGE);
+    const int visited = kept_pages + page_hi - page_lo + 1;
+    auto page_of = [&](int v) { return v < kept_pages ? v : page_lo + v - kept_pages; };
     const int* table = page_table + (size_t)b * pt_stride;
 
     const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
@@ -236,17 +249,18 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
     const bool capped = extras.cap_log2 > 0.f;
     const float scale_log2 = capped ? 1.0f : scale_log2_arg;
 
-    load_page(smem, pages, table[page_lo], G, g, HD, tid, ROWS * 2);
+    load_page(smem, pages, table[page_of(0)], G, g, HD, tid, ROWS * 2);
     cp_async_commit();
-    for (int p = page_lo; p <= page_hi; ++p) {
-        const int cur = (p - page_lo) & 1;
-        if (p + 1 <= page_hi) load_page(smem + (cur ^ 1) * STAGE, pages, table[p + 1], G, g, HD, tid, ROWS * 2);
+    for (int vp = 0; vp < visited; ++vp) {
+        const int p = page_of(vp);
+        const int cur = vp & 1;
+        if (vp + 1 < visited) load_page(smem + (cur ^ 1) * STAGE, pages, table[page_of(vp + 1)], G, g, HD, tid, ROWS * 2);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
         const int key_base = p * PAGE;
         const bool active = key_base <= warp_last_pos &&
-                            (window <= 0 || key_base + PAGE - 1 > warp_first_pos - window);
+                            (window <= 0 || key_base + PAGE - 1 > warp_first_pos - window || key_base < keep);
         if (active) {
             const uint32_t k_tile = smem_u32(smem + cur * STAGE);
             const uint32_t v_tile = k_tile + TILE;
@@ -278,7 +292,7 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
                     for (int e = 0; e < 4; ++e) {
                         const int key = key_base + nt * 8 + (lane & 3) * 2 + (e & 1);
                         const int pos = (e < 2) ? pos_lo : pos_hi;
-                        if (key > pos || (window > 0 && key <= pos - window)) s[nt][e] = -INFINITY;
+                        if (key > pos || (window > 0 && key <= pos - window && key >= keep)) s[nt][e] = -INFINITY;
                     }
             }
             float mx_lo = -INFINITY, mx_hi = -INFINITY;
@@ -443,8 +457,9 @@ int check_geometry(const char* what, int H, int G, int hd) {
 }
 
 // softcap > 0: scores are capped at it; sinks: float32 [H] or null (see ScoreExtras)
-static ScoreExtras make_extras(float scale, float softcap, const float* sinks) {
+static ScoreExtras make_extras(float scale, float softcap, const float* sinks, int keep = 0) {
     ScoreExtras x{};
+    x.keep = keep > 0 ? keep : 0;
     if (softcap > 0.f) {
         x.cap_log2 = softcap * 1.4426950408889634f;
         x.scale_over_cap = scale / softcap;
@@ -460,9 +475,9 @@ static ScoreExtras make_extras(float scale, float softcap, const float* sinks) {
 extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
                                     const int* q_start, const int* kv_len, int B, int max_new, int H, int G, int hd,
                                     int page_size, float scale, int window, float softcap, const float* sinks,
-                                    int split_weights, cudaStream_t stream) {
+                                    int split_weights, int keep, cudaStream_t stream) {
     if (B <= 0 || max_new <= 0) return 0;
-    const ScoreExtras extras = make_extras(scale, softcap, sinks);
+    const ScoreExtras extras = make_extras(scale, softcap, sinks, keep);
     int rc = check_geometry("attention_prefill", H, G, hd);
     if (rc) return rc;
     if (page_size != PAGE) LP_REFUSE("attention_prefill: pages of %d positions (built for %d)", page_size, PAGE);

@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(KB)
 attention_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV* __restrict__ pages,
                        const int* __restrict__ page_table, int pt_stride, const int* __restrict__ seq_ids,
                        const int* __restrict__ positions, int H, int G, int hd, int page_size, float scale,
-                       int window, float softcap, const float* __restrict__ sinks) {
+                       int window, float softcap, const float* __restrict__ sinks, int keep) {
     __shared__ float qs[MAX_HD];
     __shared__ float prob[KB];
     __shared__ long long row_off[KB];
@@ -33,6 +33,9 @@ attention_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV
     const int seq = seq_ids[t];
     const int pos = positions[t];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    // a window may keep a sequence's first `keep` tokens visible as well: keys [0, keep_end) besides [lo, pos]
+    const int keep_end = keep < lo ? (keep > 0 ? keep : 0) : lo;
+    const int c_lo = (lo / KB) * KB;
 
     const TQ* qr = q + ((long long)t * H + h) * hd;
     for (int i = tid; i < hd; i += KB) qs[i] = lp_to_float(qr[i]);
@@ -42,9 +45,11 @@ attention_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV
     float acc0 = 0.f, acc1 = 0.f;   // features tid and tid + 128
     const int* pt = page_table + (long long)seq * pt_stride;
 
-    for (int c0 = (lo / KB) * KB; c0 <= pos; c0 += KB) {
+    for (int c0 = 0;; c0 += KB) {
+        if (c0 >= keep_end && c0 < c_lo) c0 = c_lo;      // the blocks between the kept tokens and the window are not seen
+        if (c0 > pos) break;
         const int key = c0 + tid;
-        const bool valid = key >= lo && key <= pos;
+        const bool valid = key <= pos && (key >= lo || key < keep_end);
         float sc = -INFINITY;
         if (valid) {
             const int page = pt[key / page_size];
@@ -66,15 +71,15 @@ attention_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV
         acc0 *= alpha;
         acc1 *= alpha;
         const int nk = (pos - c0 + 1 < KB) ? pos - c0 + 1 : KB;
-        const int first = lo > c0 ? lo - c0 : 0;
+        const int first = c0 < keep_end ? 0 : (lo > c0 ? lo - c0 : 0);
         const long long v_shift = (long long)G * page_size * hd;    // from a K row to its V row
         if (tid < hd) {
             for (int j = first; j < nk; ++j)
-                acc0 = fmaf(prob[j], lp_to_float(pages[row_off[j] + v_shift + tid]), acc0);
+                if (prob[j] > 0.f) acc0 = fmaf(prob[j], lp_to_float(pages[row_off[j] + v_shift + tid]), acc0);
         }
         if (tid + KB < hd) {
             for (int j = first; j < nk; ++j)
-                acc1 = fmaf(prob[j], lp_to_float(pages[row_off[j] + v_shift + tid + KB]), acc1);
+                if (prob[j] > 0.f) acc1 = fmaf(prob[j], lp_to_float(pages[row_off[j] + v_shift + tid + KB]), acc1);
         }
         m = m_new;
         __syncthreads();
@@ -98,11 +103,12 @@ attention_plain_kernel(const TQ* __restrict__ q, TQ* __restrict__ out, const TKV
 
 // q, out: [T, H, hd]; pages: [num_pages, 2, G, page_size, hd]; page_table: [B, pt_stride];
 // seq_ids, positions: [T]. window <= 0: all keys up to the query's position. softcap > 0: a score s becomes
-// softcap * tanh(s / softcap) after the scale. sinks (optional): float32 [H], see the kernel.
+// softcap * tanh(s / softcap) after the scale. sinks (optional): float32 [H], see the kernel. keep > 0 (with a window):
+// the sequence's first `keep` tokens stay visible to every later query, at their true positions.
 extern "C" int lp_attention_plain(const void* q, void* out, int q_dtype, const void* pages, int kv_dtype,
                                   const int* page_table, int pt_stride, const int* seq_ids, const int* positions,
                                   int T, int H, int G, int hd, int page_size, float scale, int window,
-                                  float softcap, const float* sinks, cudaStream_t stream) {
+                                  float softcap, const float* sinks, int keep, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G) LP_REFUSE("attention_plain: %d query heads over %d key heads", H, G);
     if (hd <= 0 || hd > MAX_HD) LP_REFUSE("attention_plain: head size %d (supported: 1..%d)", hd, MAX_HD);
@@ -112,7 +118,7 @@ extern "C" int lp_attention_plain(const void* q, void* out, int q_dtype, const v
 #define LP_LAUNCH_ATT(TQ, TKV)                                                                                 \
     attention_plain_kernel<TQ, TKV><<<grid, KB, 0, stream>>>((const TQ*)q, (TQ*)out, (const TKV*)pages,          \
                                                              page_table, pt_stride, seq_ids, positions, H, G,  \
-                                                             hd, page_size, scale, window, softcap, sinks)
+                                                             hd, page_size, scale, window, softcap, sinks, keep)
     if (q_dtype == LP_F32 && kv_dtype == LP_F32) LP_LAUNCH_ATT(float, float);
     else if (q_dtype == LP_BF16 && kv_dtype == LP_BF16) LP_LAUNCH_ATT(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == LP_F32 && kv_dtype == LP_BF16) LP_LAUNCH_ATT(float, __nv_bfloat16);

@@ -399,10 +399,11 @@ extern "C" int lp_rope_cache_write(const float* qkv, int ld, const float* inv_fr
 template <typename TOut>
 __global__ void __launch_bounds__(NORM_THREADS)
 layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
-                 TOut* __restrict__ out, int d, float eps) {
+                 TOut* __restrict__ out, int d, float eps, float* __restrict__ zero, long long zero_count) {
     __shared__ float scratch[32];
     lp_grid_release();
     lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
     const int r = blockIdx.x;
     const long long src = rows ? rows[r] : r;
     const float* xr = x + src * d;
@@ -420,14 +421,15 @@ layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, cons
     for (int i = threadIdx.x; i < d; i += NORM_THREADS) o[i] = lp_from_float<TOut>((xr[i] - mean) * scale * w[i]);
 }
 
+// zero (optional): a float32 buffer of zero_count values cleared on the side.
 extern "C" int lp_layernorm(const float* x, const int* rows, const float* w, void* out, int out_dtype, int R, int d,
-                            float eps, cudaStream_t stream) {
+                            float eps, float* zero, long long zero_count, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (d <= 0) LP_REFUSE("layernorm: width %d", d);
     if (out_dtype == LP_F32)
-        lp_launch(layernorm_kernel<float>, R, NORM_THREADS, 0, stream, x, rows, w, (float*)out, d, eps);
+        lp_launch(layernorm_kernel<float>, R, NORM_THREADS, 0, stream, x, rows, w, (float*)out, d, eps, zero, zero_count);
     else if (out_dtype == LP_BF16)
-        lp_launch(layernorm_kernel<__nv_bfloat16>, R, NORM_THREADS, 0, stream, x, rows, w, (__nv_bfloat16*)out, d, eps);
+        lp_launch(layernorm_kernel<__nv_bfloat16>, R, NORM_THREADS, 0, stream, x, rows, w, (__nv_bfloat16*)out, d, eps, zero, zero_count);
     else
         LP_REFUSE("layernorm: output dtype code %d", out_dtype);
     return lp_check_launch("layernorm");
@@ -1011,4 +1013,31 @@ extern "C" int lp_stream_cast(const float* x, void* out, int out_dtype, long lon
     else if (out_dtype == LP_BF16) lp_launch(stream_cast_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, x, (__nv_bfloat16*)out, n, zero, zero_count);
     else LP_REFUSE("stream_cast: output dtype code %d", out_dtype);
     return lp_check_launch("stream_cast");
+}
+
+// ---------------------------------------------------------------- two sublayers' results summed with constants
+// x[t, i] += sa * (a[t, i] + va[i]) + sb * (b[t, i] + vb[i]); b, va and vb may be absent. float32.
+__global__ void __launch_bounds__(256)
+scaled_sum_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ va, float sa,
+                  const float* __restrict__ b, const float* __restrict__ vb, float sb, int T, int d) {
+    lp_grid_release();
+    lp_grid_wait();
+    const long long n = (long long)T * d;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % d);
+        float v = x[i];
+        v = fmaf(sa, a[i] + (va ? va[c] : 0.f), v);
+        if (b) v = fmaf(sb, b[i] + (vb ? vb[c] : 0.f), v);
+        x[i] = v;
+    }
+}
+
+extern "C" int lp_scaled_sum(float* x, const float* a, const float* va, float sa, const float* b, const float* vb, float sb,
+                             int T, int d, cudaStream_t stream) {
+    if (T <= 0 || d <= 0) return 0;
+    const long long n = (long long)T * d;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    lp_launch(scaled_sum_kernel, (unsigned)blocks, 256, 0, stream, x, a, va, sa, b, vb, sb, T, d);
+    return lp_check_launch("scaled_sum");
 }

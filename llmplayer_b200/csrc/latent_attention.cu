@@ -32,7 +32,8 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_
                       const int* __restrict__ seq_ids, const int* __restrict__ page_table, int pt_stride,
                       float* __restrict__ q_out, TKV* __restrict__ pages, int H, int dn, int dr, int rank,
                       int page_size, __nv_bfloat16* __restrict__ latent_out, __nv_bfloat16* __restrict__ shared_out,
-                      __nv_bfloat16* __restrict__ q_half, int q_half_hd) {
+                      __nv_bfloat16* __restrict__ q_half, int q_half_hd, const float* __restrict__ q_sep, int ldq,
+                      int interleaved, float magnitude) {
     __shared__ float cs[128], sn[128];
     __shared__ float scratch[32];
     lp_grid_release();
@@ -40,7 +41,13 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_
     const int t = blockIdx.x, tid = threadIdx.x;
     const int pos = positions[t];
     const int half = rot >> 1;
-    for (int i = tid; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+    for (int i = tid; i < half; i += blockDim.x) {
+        float sv, cv;
+        sincosf((float)pos * inv_freq[i], &sv, &cv);
+        // a rotation may come with a factor on both cosine and sine (wavelength-stretched encodings)
+        sn[i] = magnitude != 1.0f ? sv * magnitude : sv;
+        cs[i] = magnitude != 1.0f ? cv * magnitude : cv;
+    }
     const float* row = proj + (long long)t * ld;
     const float* kv = row + kv_off;
     float ss = 0.f;
@@ -55,24 +62,36 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, int q_off, int kv_
         dst[i] = lp_from_float<TKV>(c);
         if (latent_out) latent_out[(long long)t * rank + i] = __float2bfloat16_rn(c);
     }
-    // the shared key part: pairs (i, i + half) of its first `rot` values turn, the rest pass
+    // the shared key part: pairs (i, i + half), or neighbours (2i, 2i + 1), of its first `rot` values turn, the rest pass
     const float* kr = kv + rank;
     for (int i = tid; i < dr; i += blockDim.x) {
         float v = kr[i];
-        if (i < half) v = __fsub_rn(__fmul_rn(kr[i], cs[i]), __fmul_rn(kr[i + half], sn[i]));
+        if (interleaved) {
+            if (i < rot) {
+                const int pr = i >> 1;
+                v = (i & 1) ? __fadd_rn(__fmul_rn(kr[i], cs[pr]), __fmul_rn(kr[i - 1], sn[pr]))
+                            : __fsub_rn(__fmul_rn(kr[i], cs[pr]), __fmul_rn(kr[i + 1], sn[pr]));
+            }
+        } else if (i < half) v = __fsub_rn(__fmul_rn(kr[i], cs[i]), __fmul_rn(kr[i + half], sn[i]));
         else if (i < rot) v = __fadd_rn(__fmul_rn(kr[i], cs[i - half]), __fmul_rn(kr[i - half], sn[i - half]));
         dst[rank + i] = lp_from_float<TKV>(v);
         if (shared_out) shared_out[(long long)t * dr + i] = __float2bfloat16_rn(v);
     }
     // queries: head by head [dn as projected | dr with the same rotation]
     const int hd = dn + dr;
-    const float* q = row + q_off;
+    const float* q = q_sep ? q_sep + (long long)t * ldq : row + q_off;      // queries may come from a product of their own
     float* qo = q_out + (long long)t * H * hd;
     for (int e = tid; e < H * hd; e += blockDim.x) {
         const int i = e % hd - dn;
         float v = q[e];
         if (i >= 0) {
-            if (i < half) v = __fsub_rn(__fmul_rn(q[e], cs[i]), __fmul_rn(q[e + half], sn[i]));
+            if (interleaved) {
+                if (i < rot) {
+                    const int pr = i >> 1;
+                    v = (i & 1) ? __fadd_rn(__fmul_rn(q[e], cs[pr]), __fmul_rn(q[e - 1], sn[pr]))
+                                : __fsub_rn(__fmul_rn(q[e], cs[pr]), __fmul_rn(q[e + 1], sn[pr]));
+                }
+            } else if (i < half) v = __fsub_rn(__fmul_rn(q[e], cs[i]), __fmul_rn(q[e + half], sn[i]));
             else if (i < rot) v = __fadd_rn(__fmul_rn(q[e], cs[i - half]), __fmul_rn(q[e - half], sn[i - half]));
         }
         qo[e] = v;
@@ -194,7 +213,8 @@ template <typename TKV, int RW, int NC>
 __global__ void __launch_bounds__(WARPS * 32)
 latent_attend_kernel(const float* __restrict__ qa, const TKV* __restrict__ pages, const int* __restrict__ page_table,
                      int pt_stride, const int* __restrict__ q_start, const int* __restrict__ kv_len,
-                     float* __restrict__ part, int H, int rank, int dr, int page_size, float scale, int shares) {
+                     float* __restrict__ part, int H, int rank, int dr, int page_size, float scale, int shares,
+                     int window) {
     extern __shared__ float smem[];
     constexpr int ROWS = WARPS * RW;
     // rows of a multiple of 4 values are read four at a time (a key row's stride of Dk + 4 floats keeps the lanes'
@@ -232,10 +252,14 @@ latent_attend_kernel(const float* __restrict__ qa, const TKV* __restrict__ pages
         for (int c = 0; c < NC; ++c) o[r][c] = 0.f;
     }
     const int last_pos = first_pos + (r0 + n_rows - 1) / H;          // the CTA's largest causal limit
-    const int blocks_seq = (len + KEYS - 1) / KEYS;
-    const int per = (blocks_seq + shares - 1) / shares;
-    const int blk_lo = share * per;
-    const int blk_hi = min(min((share + 1) * per, blocks_seq), last_pos / KEYS + 1);
+    // the key blocks that some row of the CTA can see (up to the largest causal limit, and from the start of the
+    // first row's window on) are cut into the shares
+    const int cta_first_pos = first_pos + r0 / H;
+    const int blk_first = window > 0 ? max(0, cta_first_pos - window + 1) / KEYS : 0;
+    const int blk_end = last_pos / KEYS + 1;
+    const int per = (blk_end - blk_first + shares - 1) / shares;
+    const int blk_lo = blk_first + share * per;
+    const int blk_hi = min(blk_lo + per, blk_end);
     const int* pt = page_table + (long long)b * pt_stride;
     for (int blk = blk_lo; blk < blk_hi; ++blk) {
         const int k0 = blk * KEYS;
@@ -291,7 +315,7 @@ latent_attend_kernel(const float* __restrict__ qa, const TKV* __restrict__ pages
         float p[RW];
 #pragma unroll
         for (int r = 0; r < RW; ++r) {
-            const bool seen = k0 + lane <= pos_r[r];
+            const bool seen = k0 + lane <= pos_r[r] && (window <= 0 || k0 + lane > pos_r[r] - window);
             const float sc = seen ? dot[r] * scale : -INFINITY;
             const float m_new = fmaxf(m[r], lp_warp_max(sc));
             float alpha = 1.f;
@@ -508,6 +532,26 @@ int grant_shared(K kernel, size_t bytes, const char* what) {
     return 0;
 }
 
+
+// ---------------------------------------------------------------- the queries' own latent
+// out[t, i] = x[t, off + i] / sqrt(mean_i x^2 + eps) * gain[i] for the `rank` columns from `off` of the float32
+// projection: where queries go through a latent of their own, its RMS norm in front of the queries' map.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+latent_query_norm_kernel(const float* __restrict__ proj, int ld, int off, int rank, const float* __restrict__ gain, float eps,
+                         TOut* __restrict__ out) {
+    __shared__ float scratch[32];
+    lp_grid_release();
+    lp_grid_wait();
+    const float* x = proj + (long long)blockIdx.x * ld + off;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+    ss = lp_block_sum(ss, scratch);
+    const float f = 1.0f / sqrtf(ss / (float)rank + eps);
+    TOut* o = out + (long long)blockIdx.x * rank;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) o[i] = lp_from_float<TOut>(x[i] * f * gain[i]);
+}
+
 }  // namespace
 
 // proj: float32 [T, ld] with the queries at q_off ([H, dn + dr]) and the latent and shared key part at kv_off
@@ -518,19 +562,22 @@ extern "C" int lp_latent_prepare(const float* proj, int ld, int q_off, int kv_of
                                  const float* inv_freq, int rot, const int* positions, const int* seq_ids,
                                  const int* page_table, int pt_stride, float* q_out, void* pages, int kv_dtype, int T,
                                  int H, int dn, int dr, int rank, int page_size, void* latent_out, void* shared_out,
-                                 void* q_half, int q_half_hd, cudaStream_t stream) {
+                                 void* q_half, int q_half_hd, const float* q_sep, int ldq, int interleaved,
+                                 float magnitude, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (q_sep && ldq < H * (dn + dr)) LP_REFUSE("latent_prepare: query rows of %d for %d heads of %d", ldq, H, dn + dr);
     if (H <= 0 || dn < 0 || dr < 0 || rank <= 0 || dn + dr <= 0) LP_REFUSE("latent_prepare: %d heads of %d + %d over rank %d", H, dn, dr, rank);
     if (rot < 0 || (rot & 1) || rot > dr || rot > 256) LP_REFUSE("latent_prepare: rotary width %d of %d (even, at most 256)", rot, dr);
     if (rot > 0 && !inv_freq) LP_REFUSE("latent_prepare: rotation without frequencies");
     if (page_size <= 0) LP_REFUSE("latent_prepare: page size %d", page_size);
     if (q_half && q_half_hd < dn + dr) LP_REFUSE("latent_prepare: padded heads of %d for heads of %d", q_half_hd, dn + dr);
-    if (q_off < 0 || kv_off < 0 || q_off + H * (dn + dr) > ld || kv_off + rank + dr > ld)
+    if (q_off < 0 || kv_off < 0 || (!q_sep && q_off + H * (dn + dr) > ld) || kv_off + rank + dr > ld)
         LP_REFUSE("latent_prepare: slices at %d and %d do not fit rows of %d", q_off, kv_off, ld);
 #define LP_LAUNCH_PREP(TKV)                                                                                       \
     lp_launch(latent_prepare_kernel<TKV>, T, 256, 0, stream, proj, ld, q_off, kv_off, gain, eps, inv_freq, rot,    \
               positions, seq_ids, page_table, pt_stride, q_out, (TKV*)pages, H, dn, dr, rank, page_size,                   \
-              (__nv_bfloat16*)latent_out, (__nv_bfloat16*)shared_out, (__nv_bfloat16*)q_half, q_half_hd)
+              (__nv_bfloat16*)latent_out, (__nv_bfloat16*)shared_out, (__nv_bfloat16*)q_half, q_half_hd, q_sep, ldq,    \
+              interleaved, magnitude)
     if (kv_dtype == LP_F32) LP_LAUNCH_PREP(float);
     else if (kv_dtype == LP_BF16) LP_LAUNCH_PREP(__nv_bfloat16);
     else LP_REFUSE("latent_prepare: cache dtype code %d", kv_dtype);
@@ -564,7 +611,8 @@ extern "C" int lp_latent_attend_rows() { return WARPS * ATTEND_RW; }
 // weights); q_start [B + 1], kv_len [B] (lengths after the step); max_new: most new tokens of a sequence.
 extern "C" int lp_latent_attend(const float* qa, const void* pages, int kv_dtype, const int* page_table, int pt_stride,
                                 const int* q_start, const int* kv_len, float* part, int B, int max_new, int H,
-                                int rank, int dr, int page_size, float scale, int shares, cudaStream_t stream) {
+                                int rank, int dr, int page_size, float scale, int shares, int window,
+                                cudaStream_t stream) {
     if (B <= 0 || max_new <= 0) return 0;
     if (H <= 0 || rank <= 0 || dr < 0) LP_REFUSE("latent_attend: %d heads over rank %d + %d", H, rank, dr);
     if (rank > 512) LP_REFUSE("latent_attend: rank %d (supported: up to 512)", rank);
@@ -579,7 +627,7 @@ extern "C" int lp_latent_attend(const float* qa, const void* pages, int kv_dtype
     do {                                                                                                             \
         if (grant_shared(latent_attend_kernel<TKV, ATTEND_RW, NC>, smem, "latent_attend")) return -1;                \
         lp_launch(latent_attend_kernel<TKV, ATTEND_RW, NC>, grid, WARPS * 32, smem, stream, qa, (const TKV*)pages,   \
-                  page_table, pt_stride, q_start, kv_len, part, H, rank, dr, page_size, scale, shares);              \
+                  page_table, pt_stride, q_start, kv_len, part, H, rank, dr, page_size, scale, shares, window);      \
     } while (0)
 #define LP_PICK_NC(TKV)                                  \
     do {                                                 \
@@ -677,4 +725,15 @@ extern "C" int lp_latent_gate_heads(const void* heads, const float* gate, int ld
     lp_launch(latent_gate_heads_kernel, (unsigned)blocks, 256, 0, stream, (const __nv_bfloat16*)heads, gate, ldg,
               (__nv_bfloat16*)out, T, H, hd, dv, zero, zero_count);
     return lp_check_launch("latent_gate_heads");
+}
+
+// proj: float32 [T, ld]; the latent's `rank` columns start at `off`; gain: float32 [rank]; out: [T, rank].
+extern "C" int lp_latent_query_norm(const float* proj, int ld, int off, int rank, const float* gain, float eps, void* out,
+                                    int dtype, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rank <= 0 || off < 0 || off + rank > ld) LP_REFUSE("latent_query_norm: %d columns at %d of rows of %d", rank, off, ld);
+    if (dtype == LP_F32) lp_launch(latent_query_norm_kernel<float>, T, 256, 0, stream, proj, ld, off, rank, gain, eps, (float*)out);
+    else if (dtype == LP_BF16) lp_launch(latent_query_norm_kernel<__nv_bfloat16>, T, 256, 0, stream, proj, ld, off, rank, gain, eps, (__nv_bfloat16*)out);
+    else LP_REFUSE("latent_query_norm: dtype code %d", dtype);
+    return lp_check_launch("latent_query_norm");
 }

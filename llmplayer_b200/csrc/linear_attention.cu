@@ -77,7 +77,8 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
                 float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
                 float* __restrict__ out, int H, int dk, int dv, float q_scale, int mode, int chunks, int chunk,
                 float* __restrict__ chunk_state, float* __restrict__ chunk_decay, int decay_per_head,
-                const float* __restrict__ key_gain, int ones, const float* __restrict__ bonus) {
+                const float* __restrict__ key_gain, int ones, const float* __restrict__ bonus, int qk_group,
+                const float* __restrict__ beta) {
     extern __shared__ float sm[];
     float* qs = sm;                         // [TB][dk]
     float* ks = qs + TB * dk;
@@ -114,8 +115,8 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
         for (int e = tid; e < nt * dk; e += blockDim.x) {
             const int i = e / dk, c = e - i * dk;
             const float* row = proj + (long long)(tb + i) * ld;
-            qs[e] = row[q_off + h * dk + c] * q_scale;
-            ks[e] = row[k_off + h * dk + c] * (key_gain ? key_gain[(long long)(tb + i) * H + h] : 1.0f);
+            qs[e] = row[q_off + (h / qk_group) * dk + c] * q_scale;
+            ks[e] = row[k_off + (h / qk_group) * dk + c] * (key_gain ? key_gain[(long long)(tb + i) * H + h] : 1.0f);
             as[e] = decay_per_head ? decay[(long long)(tb + i) * H + h] : decay[((long long)(tb + i) * H + h) * dk + c];
         }
         for (int e = tid; e < nt * VT; e += blockDim.x) {
@@ -135,6 +136,57 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
             const float* qi = qs + i * dk;
             const float* ki = ks + i * dk;
             const float* ai = as + i * dk;
+            if (beta) {
+                // the delta rule (one decay a per head): S <- a S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
+                // Both read-outs are taken from the state before the token, S^T k and S^T q, in one round of
+                // shuffles: the decayed S^T k is a (S^T k), and o = a (S^T q) + u (k . q).
+                float r1[JT], r2[JT], kq = 0.f;
+#pragma unroll
+                for (int jj = 0; jj < JT; ++jj) r1[jj] = r2[jj] = 0.f;
+#pragma unroll
+                for (int u = 0; u < KPT; ++u) {
+                    const int c = part + KP * u;
+                    if (c < dk) {
+                        const float k = ki[c], q = qi[c];
+                        kq = fmaf(k, q, kq);
+#pragma unroll
+                        for (int jj = 0; jj < JT; ++jj) {
+                            r1[jj] = fmaf(s[u][jj], k, r1[jj]);
+                            r2[jj] = fmaf(s[u][jj], q, r2[jj]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int o = 1; o < KP; o <<= 1) {
+                    kq += __shfl_xor_sync(0xffffffffu, kq, o);
+#pragma unroll
+                    for (int jj = 0; jj < JT; ++jj) {
+                        r1[jj] += __shfl_xor_sync(0xffffffffu, r1[jj], o);
+                        r2[jj] += __shfl_xor_sync(0xffffffffu, r2[jj], o);
+                    }
+                }
+                const float a = ai[0];
+                const float bt = beta[(long long)(tb + i) * H + h];
+                float w[JT];
+#pragma unroll
+                for (int jj = 0; jj < JT; ++jj) {
+                    w[jj] = bt * (v[jj] - a * r1[jj]);
+                    acc[jj] = fmaf(w[jj], kq, a * r2[jj]);
+                }
+#pragma unroll
+                for (int u = 0; u < KPT; ++u) {
+                    const int c = part + KP * u;
+                    if (c < dk) {
+                        const float k = ki[c];
+#pragma unroll
+                        for (int jj = 0; jj < JT; ++jj) s[u][jj] = fmaf(a, s[u][jj], k * w[jj]);
+                    }
+                }
+#pragma unroll
+                for (int jj = 0; jj < JT; ++jj)
+                    if (part == jj % KP && j0 + jj < dv) out[((long long)(tb + i) * H + h) * dv + j0 + jj] = acc[jj];
+                continue;
+            }
 #pragma unroll
             for (int u = 0; u < KPT; ++u) {
                 const int c = part + KP * u;
@@ -381,6 +433,148 @@ gla_finish_kernel(const float* __restrict__ o, const float* __restrict__ gain, f
     }
 }
 
+
+// ---------------------------------------------------------------- short causal convolution with a carried tail
+// out[t, c] = act(bias[c] + sum_j taps[c, j] * in[t - (K - 1) + j, c]), K taps per channel, the last one on the token
+// itself; inputs before a sequence's first token are zero, inputs before the step's first token come from the K - 1
+// rows kept for the sequence's slot in `tail` [slots, K - 1, C] (oldest first), which afterwards holds the step's
+// last K - 1 inputs. grid (channels / 128, chunks of CONV_CHUNK tokens, sequences): a thread owns one channel of one
+// chunk and walks its tokens in order with the K - 1 inputs before them in registers. Only a sequence's first chunk
+// reads the tail (CONV_CHUNK >= K - 1), and the same thread, having read it, writes the new one.
+constexpr int CONV_CHUNK = 32;
+constexpr int CONV_MAX_TAPS = 8;
+
+template <typename TW>
+__global__ void __launch_bounds__(128)
+short_conv_kernel(const float* __restrict__ in, int ldi, const TW* __restrict__ taps, const float* __restrict__ bias,
+                  float* __restrict__ tail, const int* __restrict__ slots, const int* __restrict__ q_start,
+                  float* __restrict__ out, int ldo, int C, int K, int silu) {
+    lp_grid_release();
+    lp_grid_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.z;
+    const int t0 = q_start[b], t1 = q_start[b + 1];
+    const int begin = t0 + blockIdx.y * CONV_CHUNK;
+    if (c >= C || begin >= t1) return;
+    const int end = min(t1, begin + CONV_CHUNK);
+    // taps and the inputs before the token, both aligned at their ends: w[7] multiplies the token itself, w[6] and
+    // hist[6] belong to the token before it, and so on; taps beyond K are zero, so all seven places always take part
+    float w[CONV_MAX_TAPS], hist[CONV_MAX_TAPS - 1];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+        const int tap = j - (CONV_MAX_TAPS - K);
+        w[j] = tap >= 0 ? lp_to_float(taps[(long long)c * K + tap]) : 0.f;
+    }
+    float* keep = tail + (long long)slots[b] * (K - 1) * C + c;
+#pragma unroll
+    for (int i = 0; i < CONV_MAX_TAPS - 1; ++i) {               // hist[6 - i]: the input i + 1 tokens before `begin`
+        float v = 0.f;
+        if (i < K - 1) {
+            const int src = begin - 1 - i;
+            v = src >= t0 ? in[(long long)src * ldi + c] : keep[(long long)(K - 1 + src - t0) * C];
+        }
+        hist[CONV_MAX_TAPS - 2 - i] = v;
+    }
+    if (begin == t0) {
+        // the step's last K - 1 inputs become the tail: new tokens where there are enough, else older rows move up
+        // (row j takes row j + n, which is still unwritten when row j is)
+        const int n = t1 - t0;
+        for (int j = 0; j < K - 1; ++j) {
+            const int src = t1 - (K - 1) + j;                  // token index of the j-th row of the new tail
+            keep[(long long)j * C] = src >= t0 ? in[(long long)src * ldi + c] : keep[(long long)(j + n) * C];
+        }
+    }
+    const float bv = bias ? bias[c] : 0.f;
+    for (int t = begin; t < end; ++t) {
+        const float x = in[(long long)t * ldi + c];
+        float acc = bv;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) acc = fmaf(w[j], hist[j], acc);
+        acc = fmaf(w[CONV_MAX_TAPS - 1], x, acc);
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 2; ++j) hist[j] = hist[j + 1];
+        hist[CONV_MAX_TAPS - 2] = x;
+        out[(long long)t * ldo + c] = silu ? acc / (1.0f + expf(-acc)) : acc;
+    }
+}
+
+// ---------------------------------------------------------------- step sizes, decays and write strengths of a recurrence
+// Per token and head, from float32 columns of a projection: dt = softplus(z + dt_bias[h]) (no clamp),
+// decay = exp(-exp(a_log[h]) * dt), and, where a second column zb is given, strength = sigmoid(zb).
+__global__ void __launch_bounds__(256)
+decay_gates_kernel(const float* __restrict__ proj, int ld, int z_off, int b_off, const float* __restrict__ dt_bias,
+                   const float* __restrict__ a_log, float* __restrict__ decay, float* __restrict__ dt_out,
+                   float* __restrict__ strength, int T, int H) {
+    lp_grid_release();
+    lp_grid_wait();
+    const long long n = (long long)T * H;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / H;
+        const int h = (int)(i - t * H);
+        const float z = proj[t * ld + z_off + h] + (dt_bias ? dt_bias[h] : 0.f);
+        const float dt = z > 20.f ? z : log1pf(expf(z));
+        decay[i] = expf(-expf(a_log[h]) * dt);
+        if (dt_out) dt_out[i] = dt;
+        if (strength) strength[i] = 1.0f / (1.0f + expf(-proj[t * ld + b_off + h]));
+    }
+}
+
+// ---------------------------------------------------------------- heads made unit vectors
+// x[t, off + h * dim + i] <- x / sqrt(sum_i x^2 + eps), in place, float32; the first `scaled` heads also times `scale`
+// (queries in front of keys). A warp per (token, head).
+__global__ void __launch_bounds__(128)
+head_unit_norm_kernel(float* __restrict__ x, int ld, int off, int heads, int dim, float eps, float scale, int scaled, int T) {
+    lp_grid_release();
+    lp_grid_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * 4 + warp;
+    if (row >= (long long)T * heads) return;
+    const long long t = row / heads;
+    const int h = (int)(row - t * heads);
+    float* v = x + t * ld + off + (long long)h * dim;
+    float ss = 0.f;
+    for (int i = lane; i < dim; i += 32) ss = fmaf(v[i], v[i], ss);
+    ss = lp_warp_sum(ss);
+    const float f = (h < scaled ? scale : 1.0f) / sqrtf(ss + eps);
+    for (int i = lane; i < dim; i += 32) v[i] *= f;
+}
+
+// ---------------------------------------------------------------- skip, gate, then a norm in equal parts
+// y[t, h * P + i] = (raw[t, h * P + i] + skip[h] * x[t, h * P + i]) * silu(z[t, h * P + i]); the row of H * P values is
+// then cut into `parts` equal parts, each divided by its own root mean square (eps inside the root) and multiplied by
+// the gain. One block per (token, part). The gate comes before the norm.
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+gated_part_norm_kernel(const float* __restrict__ raw, const float* __restrict__ x, int ldx, const float* __restrict__ skip,
+                       const float* __restrict__ z, int ldz, const float* __restrict__ gain, float eps, TOut* __restrict__ out,
+                       int P, int width, int part_width, float* __restrict__ zero, long long zero_count) {
+    __shared__ float scratch[32];
+    lp_grid_release();
+    lp_grid_wait();
+    clear_on_the_side(zero, zero_count);
+    const long long t = blockIdx.x;
+    const int base = blockIdx.y * part_width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < part_width; i += blockDim.x) {
+        const int col = base + i;
+        const float g = z[t * ldz + col];
+        float y = raw[t * width + col];
+        if (skip) y = fmaf(skip[col / P], x[t * ldx + col], y);
+        y *= g / (1.0f + expf(-g));
+        ss = fmaf(y, y, ss);
+    }
+    ss = lp_block_sum(ss, scratch);
+    const float f = 1.0f / sqrtf(ss / (float)part_width + eps);
+    for (int i = threadIdx.x; i < part_width; i += blockDim.x) {
+        const int col = base + i;
+        const float g = z[t * ldz + col];
+        float y = raw[t * width + col];
+        if (skip) y = fmaf(skip[col / P], x[t * ldx + col], y);
+        y *= g / (1.0f + expf(-g));
+        out[t * width + col] = lp_from_float<TOut>(y * f * gain[col]);
+    }
+}
+
 }  // namespace
 
 // form 0: sigmoid(z)^(1 / tau) with z = a2 low + bias; form 1: exp(-exp(z)) with z = a2 tanh(low) + bias (tau unused).
@@ -409,16 +603,23 @@ extern "C" int lp_gla_decay(const float* low, int ldl, const void* a2, int w_dty
 extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay, float* state,
                            const int* slots, const int* q_start, float* out, int B, int H, int dk, int dv,
                            float q_scale, int chunks, int chunk, float* chunk_state, float* chunk_decay,
-                           int decay_per_head, const float* key_gain, int ones, const float* bonus, cudaStream_t stream) {
+                           int decay_per_head, const float* key_gain, int ones, const float* bonus, int qk_heads,
+                           const float* beta, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (chunks < 1) chunks = 1;
+    // queries and keys may have fewer heads than the values: head h then reads query / key head h / (H / qk_heads)
+    if (qk_heads <= 0) qk_heads = H;
+    if (H % qk_heads) LP_REFUSE("gla_scan: %d heads over %d query / key heads", H, qk_heads);
+    const int qk_group = H / qk_heads;
+    if (beta && (chunks > 1 || !decay_per_head || bonus || ones))
+        LP_REFUSE("gla_scan: the delta rule runs in one pass with one decay per head (chunks %d)", chunks);
     ones = ones ? 1 : 0;
     if (dv - ones <= 0) LP_REFUSE("gla_scan: %d value columns, %d of them constant", dv, ones);
     if (chunks > 1 && (chunk <= 0 || !chunk_state || !chunk_decay)) LP_REFUSE("gla_scan: %d chunks without their buffers", chunks);
     if ((long long)B * chunks > 65535) LP_REFUSE("gla_scan: %d sequences in %d chunks exceed the grid", B, chunks);
     if (H <= 0 || H > 65535 || B > 65535 || dk <= 0 || dv <= 0) LP_REFUSE("gla_scan: %d sequences, %d heads of %d x %d", B, H, dk, dv);
     if (dk > 512) LP_REFUSE("gla_scan: %d key channels per head (supported: up to 512)", dk);
-    if (q_off < 0 || k_off < 0 || v_off < 0 || q_off + H * dk > ld || k_off + H * dk > ld || v_off + H * (dv - (ones ? 1 : 0)) > ld)
+    if (q_off < 0 || k_off < 0 || v_off < 0 || q_off + qk_heads * dk > ld || k_off + qk_heads * dk > ld || v_off + H * (dv - (ones ? 1 : 0)) > ld)
         LP_REFUSE("gla_scan: slices at %d, %d, %d do not fit rows of %d", q_off, k_off, v_off, ld);
 #define LP_LAUNCH_SCAN(KP_, VT_, N, JT_)                                                                                 \
     do {                                                                                                              \
@@ -431,17 +632,17 @@ extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
         if (chunks == 1) {                                                                                            \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_WHOLE, 1, 0, (float*)nullptr,       \
-                      (float*)nullptr, decay_per_head, key_gain, ones, bonus);                                                                               \
+                      (float*)nullptr, decay_per_head, key_gain, ones, bonus, qk_group, beta);                                                                               \
         } else {                                                                                                      \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_LOCAL, chunks, chunk, chunk_state,  \
-                      chunk_decay, decay_per_head, key_gain, ones, bonus);                                                                                   \
+                      chunk_decay, decay_per_head, key_gain, ones, bonus, qk_group, beta);                                                                                   \
             const long long per = (long long)H * dv * dk;                                                             \
             lp_launch(gla_combine_kernel, dim3((unsigned)((per + 255) / 256), B), 256, 0, stream, state, slots,       \
                       q_start, chunk_state, (const float*)chunk_decay, H, dk, dv, chunks, chunk);                     \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_OUTPUT, chunks, chunk, chunk_state, \
-                      chunk_decay, decay_per_head, key_gain, ones, bonus);                                                                                   \
+                      chunk_decay, decay_per_head, key_gain, ones, bonus, qk_group, beta);                                                                                   \
         }                                                                                                             \
     } while (0)
     // few key channels: 4 threads per column, 64 columns per CTA; from 32 channels on: 16 threads per column, 16 columns
@@ -505,4 +706,59 @@ extern "C" int lp_token_shift(const float* x, float* last, const float* mu, cons
     else if (out_dtype == LP_BF16) lp_launch(token_shift_kernel<__nv_bfloat16>, T, 256, 0, stream, x, last, mu, slots, q_start, seq_ids, (__nv_bfloat16*)out, T, d, S, zero, zero_count);
     else LP_REFUSE("token_shift: output dtype code %d", out_dtype);
     return lp_check_launch("token_shift");
+}
+
+// in: float32 [T, ldi] (C channels from the given pointer); taps: [C, K]; bias: float32 [C] or null; tail: float32
+// [slots, K - 1, C]; out: float32 [T, ldo]. max_new: most new tokens of a sequence of the step.
+extern "C" int lp_short_conv(const float* in, int ldi, const void* taps, int w_dtype, const float* bias, float* tail,
+                             const int* slots, const int* q_start, float* out, int ldo, int B, int max_new, int C, int K,
+                             int silu, cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0 || C <= 0) return 0;
+    if (K < 1 || K > CONV_MAX_TAPS) LP_REFUSE("short_conv: %d taps (supported: 1..%d)", K, CONV_MAX_TAPS);
+    if (ldi < C || ldo < C) LP_REFUSE("short_conv: rows of %d and %d values for %d channels", ldi, ldo, C);
+    const int chunks = (max_new + CONV_CHUNK - 1) / CONV_CHUNK;
+    if (chunks > 65535 || B > 65535) LP_REFUSE("short_conv: %d chunks of tokens, %d sequences exceed the grid", chunks, B);
+    dim3 grid((C + 127) / 128, chunks, B);
+    if (w_dtype == LP_F32) lp_launch(short_conv_kernel<float>, grid, 128, 0, stream, in, ldi, (const float*)taps, bias, tail, slots, q_start, out, ldo, C, K, silu);
+    else if (w_dtype == LP_BF16) lp_launch(short_conv_kernel<__nv_bfloat16>, grid, 128, 0, stream, in, ldi, (const __nv_bfloat16*)taps, bias, tail, slots, q_start, out, ldo, C, K, silu);
+    else LP_REFUSE("short_conv: dtype code %d of the taps", w_dtype);
+    return lp_check_launch("short_conv");
+}
+
+// proj: float32 [T, ld]; z_off: column of the H step-size pre-activations; b_off: column of the H write-strength
+// pre-activations (used only with `strength`); decay, dt_out (optional), strength (optional): float32 [T, H].
+extern "C" int lp_decay_gates(const float* proj, int ld, int z_off, int b_off, const float* dt_bias, const float* a_log,
+                              float* decay, float* dt_out, float* strength, int T, int H, cudaStream_t stream) {
+    if (T <= 0 || H <= 0) return 0;
+    if (z_off < 0 || z_off + H > ld || (strength && (b_off < 0 || b_off + H > ld))) LP_REFUSE("decay_gates: columns at %d / %d of rows of %d", z_off, b_off, ld);
+    long long blocks = ((long long)T * H + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    lp_launch(decay_gates_kernel, (unsigned)blocks, 256, 0, stream, proj, ld, z_off, b_off, dt_bias, a_log, decay, dt_out, strength, T, H);
+    return lp_check_launch("decay_gates");
+}
+
+extern "C" int lp_head_unit_norm(float* x, int ld, int off, int heads, int dim, float eps, float scale, int scaled, int T,
+                                 cudaStream_t stream) {
+    if (T <= 0 || heads <= 0 || dim <= 0) return 0;
+    if (off < 0 || off + heads * dim > ld) LP_REFUSE("head_unit_norm: %d heads of %d at column %d of rows of %d", heads, dim, off, ld);
+    const long long rows = (long long)T * heads;
+    lp_launch(head_unit_norm_kernel, (unsigned)((rows + 3) / 4), 128, 0, stream, x, ld, off, heads, dim, eps, scale, scaled, T);
+    return lp_check_launch("head_unit_norm");
+}
+
+// raw: float32 [T, H * P]; x: float32 [T, ldx] (the values, for the skip) with skip float32 [H], both or neither;
+// z: float32 [T, ldz] gate pre-activations; gain: float32 [H * P]; out: [T, H * P]; parts: equal parts of a row.
+extern "C" int lp_gated_part_norm(const float* raw, const float* x, int ldx, const float* skip, const float* z, int ldz,
+                                  const float* gain, float eps, void* out, int dtype, int T, int H, int P, int parts,
+                                  float* zero, long long zero_count, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const int width = H * P;
+    if (H <= 0 || P <= 0 || parts <= 0 || width % parts || parts > 65535) LP_REFUSE("gated_part_norm: %d heads of %d in %d parts", H, P, parts);
+    if ((skip != nullptr) != (x != nullptr)) LP_REFUSE("gated_part_norm: a skip comes with the values it multiplies");
+    if (ldz < width || (x && ldx < width)) LP_REFUSE("gated_part_norm: rows of %d / %d values for %d columns", ldz, ldx, width);
+    dim3 grid(T, parts);
+    if (dtype == LP_F32) lp_launch(gated_part_norm_kernel<float>, grid, 256, 0, stream, raw, x, ldx, skip, z, ldz, gain, eps, (float*)out, P, width, width / parts, zero, zero_count);
+    else if (dtype == LP_BF16) lp_launch(gated_part_norm_kernel<__nv_bfloat16>, grid, 256, 0, stream, raw, x, ldx, skip, z, ldz, gain, eps, (__nv_bfloat16*)out, P, width, width / parts, zero, zero_count);
+    else LP_REFUSE("gated_part_norm: dtype code %d", dtype);
+    return lp_check_launch("gated_part_norm");
 }

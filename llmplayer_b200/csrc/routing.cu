@@ -219,6 +219,95 @@ expert_act_vec4_kernel(const float* __restrict__ z, int ldz, int total, __nv_bfl
     }
 }
 
+
+// A third rule: scores s = softmax(z) over all E router outputs. The choice is made on s[e] + correction[e]: the
+// experts form `groups` equal groups of neighbours, a group's score is its largest choice score, only experts of the
+// `keep` best groups may be chosen (the others count as minus infinity: choice scores may be negative), and the `top`
+// largest choice scores among those win. The weights are the chosen experts' scores s themselves (without the
+// correction) times `scale`; they are not renormalised. A warp per token; among equal scores the lower index wins.
+__global__ void __launch_bounds__(128)
+route_softmax_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ correction, float* __restrict__ weights,
+                     int ldw, int T, int E, int groups, int keep, int top, float scale) {
+    extern __shared__ float sm[];
+    lp_grid_release();
+    lp_grid_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long t = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    float* s = sm + (size_t)warp * (3 * E + groups);
+    float* choice = s + E;
+    float* flag = choice + E;
+    float* gs = flag + E;
+    const int per = E / groups;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[t * ldz + e]);
+    mx = lp_warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        const float v = expf(z[t * ldz + e] - mx);
+        s[e] = v;
+        sum += v;
+    }
+    sum = lp_warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) {
+        const float v = s[e] * inv;
+        s[e] = v;
+        choice[e] = v + (correction ? correction[e] : 0.f);
+        flag[e] = groups > 1 ? 0.f : 1.f;
+    }
+    __syncwarp();
+    if (groups > 1) {
+        for (int g = lane; g < groups; g += 32) {
+            float a = -INFINITY;
+            for (int j = 0; j < per; ++j) a = fmaxf(a, choice[g * per + j]);
+            gs[g] = a;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            for (int n = 0; n < keep; ++n) {
+                int best = -1;
+                float bv = -INFINITY;
+                for (int g = 0; g < groups; ++g)
+                    if (gs[g] > bv) { bv = gs[g]; best = g; }
+                if (best < 0) break;
+                gs[best] = -INFINITY;
+                for (int j = 0; j < per; ++j) flag[best * per + j] = 1.f;
+            }
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        for (int n = 0; n < top; ++n) {
+            int best = -1;
+            float bv = -INFINITY;
+            for (int e = 0; e < E; ++e)
+                if (flag[e] == 1.f && choice[e] > bv) { bv = choice[e]; best = e; }
+            if (best < 0) break;
+            flag[best] = 2.f;
+        }
+    }
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) weights[t * ldw + e] = flag[e] == 2.f ? s[e] * scale : 0.f;
+}
+
+// x[t, :] += h[t, :] * sum_{e in [first, first + count)} weights[t, e]: experts that are the identity pass the
+// feed-forward's input on, times their weight. x float32 [T, d]; h [T, d] in the activations' format.
+template <typename TH>
+__global__ void __launch_bounds__(256)
+identity_experts_kernel(float* __restrict__ x, const TH* __restrict__ h, const float* __restrict__ weights, int ldw, int first,
+                        int count, int T, int d) {
+    lp_grid_release();
+    lp_grid_wait();
+    const long long n = (long long)T * d;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / d;
+        float w = 0.f;
+        for (int e = 0; e < count; ++e) w += weights[t * ldw + first + e];
+        if (w != 0.f) x[i] = fmaf(lp_to_float(h[i]), w, x[i]);
+    }
+}
+
 }  // namespace
 
 // z: float32 [T, ldz] (E logits per row); weights: float32 [T, ldw], E values per row written.
@@ -293,4 +382,32 @@ extern "C" int lp_expert_act(const float* z, int ldz, int total, void* hidden, i
     else if (dtype == LP_BF16) lp_launch(expert_act_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, z, ldz, total, (__nv_bfloat16*)hidden, weights, ldw, T, E, ff, limit, limit_rest, zero, zero_count);
     else LP_REFUSE("expert_act: dtype code %d", dtype);
     return lp_check_launch("expert_act");
+}
+
+// z: float32 [T, ldz], E router outputs per row; correction: float32 [E] or null; weights: float32 [T, ldw].
+extern "C" int lp_route_softmax(const float* z, int ldz, const float* correction, float* weights, int ldw, int T, int E,
+                                int groups, int keep, int top, float scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || groups <= 0 || E % groups) LP_REFUSE("route_softmax: %d experts in %d groups", E, groups);
+    if (keep <= 0 || keep > groups) LP_REFUSE("route_softmax: %d of %d groups kept", keep, groups);
+    if (top <= 0 || top > keep * (E / groups)) LP_REFUSE("route_softmax: %d experts chosen from %d groups of %d", top, keep, E / groups);
+    if (ldz < E || ldw < E) LP_REFUSE("route_softmax: rows of %d and %d values for %d experts", ldz, ldw, E);
+    const size_t smem = (size_t)4 * (3 * E + groups) * sizeof(float);
+    if (smem > 48 * 1024) LP_REFUSE("route_softmax: %d experts need %zu bytes of shared memory", E, smem);
+    lp_launch(route_softmax_kernel, (unsigned)((T + 3) / 4), 128, smem, stream, z, ldz, correction, weights, ldw, T, E, groups,
+              keep, top, scale);
+    return lp_check_launch("route_softmax");
+}
+
+// x: float32 [T, d]; h: [T, d] (dtype code); weights: float32 [T, ldw]; columns first .. first + count - 1 are summed.
+extern "C" int lp_identity_experts(float* x, const void* h, int dtype, const float* weights, int ldw, int first, int count,
+                                   int T, int d, cudaStream_t stream) {
+    if (T <= 0 || d <= 0 || count <= 0) return 0;
+    if (first < 0 || first + count > ldw) LP_REFUSE("identity_experts: columns %d..%d of rows of %d", first, first + count - 1, ldw);
+    long long blocks = ((long long)T * d + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == LP_F32) lp_launch(identity_experts_kernel<float>, (unsigned)blocks, 256, 0, stream, x, (const float*)h, weights, ldw, first, count, T, d);
+    else if (dtype == LP_BF16) lp_launch(identity_experts_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, x, (const __nv_bfloat16*)h, weights, ldw, first, count, T, d);
+    else LP_REFUSE("identity_experts: dtype code %d", dtype);
+    return lp_check_launch("identity_experts");
 }

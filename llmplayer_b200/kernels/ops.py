@@ -24,7 +24,8 @@ _P, _I, _F = c_void_p, c_int, c_float
 _SIGNATURES = {
     "elementwise": {
         "lp_embed": [_P, _I, _P, _P, _I, _I, _F, _P],
-        "lp_layernorm": [_P, _P, _P, _P, _I, _I, _I, _F, _P],
+        "lp_layernorm": [_P, _P, _P, _P, _I, _I, _I, _F, _P, ctypes.c_longlong, _P],
+        "lp_scaled_sum": [_P, _P, _P, _F, _P, _P, _F, _I, _I, _P],
         "lp_xielu": [_P, _I, _P, _P, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "lp_gated_sum": [_P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
         "lp_rmsnorm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P, ctypes.c_longlong, _P],
@@ -44,12 +45,14 @@ _SIGNATURES = {
         "lp_expert_scale": [_P, _I, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "lp_route_top": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
         "lp_expert_act": [_P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P, ctypes.c_longlong, _P],
+        "lp_route_softmax": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
+        "lp_identity_experts": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
     },
     "gemm_plain": {
         "lp_gemm_plain": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "attention_plain": {
-        "lp_attention_plain": [_P, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _F, _P, _P],
+        "lp_attention_plain": [_P, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _F, _P, _I, _P],
     },
     "gemm_tcgen05": {
         "lp_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P,
@@ -60,7 +63,7 @@ _SIGNATURES = {
         "lp_gemm_qkv_rope": [_P, _P, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     },
     "attention_mma": {
-        "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _F, _P, _I, _P],
+        "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _F, _P, _I, _I, _P],
         "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
         "lp_attention_decode_fitted": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
         "lp_attention_decode_fused": [_P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
@@ -72,18 +75,23 @@ _SIGNATURES = {
     },
     "latent_attention": {
         "lp_latent_prepare": [_P, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P,
-                              _I, _P],
+                              _I, _P, _I, _I, _F, _P],
         "lp_latent_heads_to_pages": [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "lp_latent_gate_heads": [_P, _P, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "lp_latent_absorb": [_P, _P, _I, _P, _I, _I, _I, _I, _I, _P],
         "lp_latent_attend_rows": [],
-        "lp_latent_attend": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "lp_latent_attend": [_P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
         "lp_latent_merge": [_P, _I, _P, _I, _I, _P],
+        "lp_latent_query_norm": [_P, _I, _I, _I, _P, _F, _P, _I, _I, _P],
         "lp_latent_expand": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
     },
     "linear_attention": {
         "lp_gla_decay": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _F, _I, _P],
-        "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _I, _P, _P],
+        "lp_gla_scan": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _I, _P, _I, _P, _I, _P, _P],
+        "lp_short_conv": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "lp_decay_gates": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _I, _I, _P],
+        "lp_head_unit_norm": [_P, _I, _I, _I, _I, _F, _F, _I, _I, _P],
+        "lp_gated_part_norm": [_P, _P, _I, _P, _P, _I, _P, _F, _P, _I, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "lp_token_shift": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
         "lp_gla_finish": [_P, _P, _F, _P, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _I, _I, _I, _P, _P],
         "lp_exp_gates": [_P, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _P],
@@ -398,9 +406,9 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 
 
 def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+              rows: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[r] = (x[rows[r]] - mean) / sqrt(variance + eps) * weight, float32 inside; the variance is the mean
-    of the squared deviations from the mean."""
+    of the squared deviations from the mean. ``clear``: a float32 buffer zeroed on the side."""
     _want(x, "layernorm x", torch.float32, 2)
     _want(weight, "layernorm weight", torch.float32, 1)
     _want(out, "layernorm out", ndim=2)
@@ -415,7 +423,7 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tens
         raise KernelError(f"layernorm: x {tuple(x.shape)} and out {tuple(out.shape)} differ in rows")
     lib = library("elementwise")
     _check(lib, lib.lp_layernorm(x.data_ptr(), _ptr(rows), weight.data_ptr(), out.data_ptr(), _code(out, "layernorm out"),
-                                 R, d, float(eps), _stream()))
+                                 R, d, float(eps), *_clear_args(clear, "layernorm"), _stream()))
     return out
 
 
@@ -513,9 +521,12 @@ class Rotation:
     inv_freq: Optional[torch.Tensor] = None      # float32 [rotary_dim / 2] on the device
     rotary_dim: int = 0
     interleaved: bool = False
+    magnitude: float = 1.0                       # a factor on both cosine and sine (wavelength-stretched encodings)
 
-    def checked(self, what: str):
+    def checked(self, what: str, takes_magnitude: bool = False):
         """(pointer or None, rotary_dim, interleaved as int) after checking the frequencies."""
+        if self.magnitude != 1.0 and not takes_magnitude:
+            raise KernelError(f"{what}: a rotation with a factor of {self.magnitude} on cosine and sine is not supported here")
         if self.rotary_dim <= 0:
             return None, 0, 0
         _want(self.inv_freq, f"{what} inv_freq", torch.float32, 1)
@@ -574,7 +585,7 @@ QKV_ROPE_HEAD_SIZES = (32, 64, 128, 256)
 
 def qkv_rope_serves(rotation: Rotation, head_dim: int) -> bool:
     """Whether :func:`gemm_qkv_rope` can apply this rotation to heads of this size in its epilogue."""
-    if head_dim not in QKV_ROPE_HEAD_SIZES or rotation.rotary_dim not in (0, head_dim):
+    if head_dim not in QKV_ROPE_HEAD_SIZES or rotation.rotary_dim not in (0, head_dim) or rotation.magnitude != 1.0:
         return False
     return rotation.rotary_dim == 0 or rotation.interleaved or head_dim >= 64
 
@@ -849,10 +860,11 @@ def gemm_few(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ST
 def attention_plain(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
                     seq_ids: torch.Tensor, positions: torch.Tensor, *, num_heads: int, num_kv_heads: int,
                     head_dim: int, scale: float, window: Optional[int], softcap: Optional[float] = None,
-                    sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    sinks: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
     """Each query token attends over the cached keys of its sequence up to its own
     position (and within ``window``, if given). ``softcap``: scores become softcap * tanh(score / softcap) after the
-    scale; ``sinks``: float32 [H], a logit per head that enters the softmax's denominator once."""
+    scale; ``sinks``: float32 [H], a logit per head that enters the softmax's denominator once. ``keep_first`` (with a
+    window): the sequence's first ``keep_first`` tokens stay visible to every later query."""
     _check_sinks(sinks, num_heads, "attention")
     _want(q, "attention q", ndim=2)
     _want(out, "attention out", q.dtype, 2)
@@ -870,7 +882,8 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pag
     _check(lib, lib.lp_attention_plain(
         q.data_ptr(), out.data_ptr(), _code(q, "attention q"), pages.data_ptr(), _code(pages, "attention pages"),
         page_table.data_ptr(), page_table.shape[1], seq_ids.data_ptr(), positions.data_ptr(), T, H, G, hd,
-        pages.shape[3], float(scale), int(window) if window else 0, float(softcap or 0.0), _ptr(sinks), _stream()))
+        pages.shape[3], float(scale), int(window) if window else 0, float(softcap or 0.0), _ptr(sinks),
+        int(keep_first) if window else 0, _stream()))
     return out
 
 
@@ -899,8 +912,9 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
                       q_start: torch.Tensor, kv_len: torch.Tensor, max_new: int, *, num_heads: int,
                       num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
                       softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
-                      exact_weights: bool = False) -> torch.Tensor:
-    """Tensor-core attention for a step that brings several tokens per sequence.
+                      exact_weights: bool = False, keep_first: int = 0) -> torch.Tensor:
+    """Tensor-core attention for a step that brings several tokens per sequence. ``keep_first`` (with a window): the
+    sequence's first ``keep_first`` tokens stay visible to every later query.
     ``q_start`` [B+1]: offsets of each sequence's new tokens; ``kv_len`` [B]: lengths after the step.
     ``exact_weights``: the softmax weights enter the product with the values at float32 precision (as a bfloat16
     value plus a bfloat16 rest, two products) instead of rounded to bfloat16."""
@@ -911,7 +925,9 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
     if q_start.numel() != B + 1 or page_table.shape[0] != B:
         raise KernelError(f"attention_prefill: {B} sequences, {q_start.numel()} offsets, table {tuple(page_table.shape)}")
     _check_sinks(sinks, num_heads, "attention_prefill")
-    if head_dim in (64, 128) and max_new > 64 and tcgen05_attention and not softcap and sinks is None and not exact_weights:
+    keep_first = int(keep_first) if window else 0
+    if (head_dim in (64, 128) and max_new > 64 and tcgen05_attention and not softcap and sinks is None and not exact_weights
+            and not keep_first):
         # long runs of new tokens with heads of 64 or 128: scores and P V on the tcgen05 tensor cores
         lib = library("attention_tcgen05")
         _check(lib, lib.lp_attention_prefill_tc(
@@ -924,7 +940,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
     _check(lib, lib.lp_attention_prefill(
         q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         q_start.data_ptr(), kv_len.data_ptr(), B, int(max_new), num_heads, num_kv_heads, head_dim, pages.shape[3],
-        float(scale), int(window) if window else 0, float(softcap or 0.0), _ptr(sinks), 1 if exact_weights else 0, _stream()))
+        float(scale), int(window) if window else 0, float(softcap or 0.0), _ptr(sinks), 1 if exact_weights else 0,
+        keep_first, _stream()))
     return out
 
 
@@ -1041,21 +1058,25 @@ def attention_decode_fused(qkv: torch.Tensor, rotation: Rotation, out: torch.Ten
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor, *,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
               fast: bool, softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
-              exact_weights: bool = False) -> torch.Tensor:
-    """Attention of the step's tokens over the cache; picks the kernel for the step's shape."""
+              exact_weights: bool = False, keep_first: int = 0) -> torch.Tensor:
+    """Attention of the step's tokens over the cache; picks the kernel for the step's shape. ``keep_first`` (with a
+    window): the first tokens of a sequence that stay visible beyond the window; one-token steps of such a layer run
+    on the plain kernel (a block per token and head walks the kept tokens and the window)."""
     tensor_cores = (fast and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
                     and head_dim % 16 == 0 and head_dim <= 256)
-    if tensor_cores and ctx.all_single:
+    keep_first = int(keep_first) if window else 0
+    if tensor_cores and ctx.all_single and not keep_first:
         return attention_decode(q, out, pages, page_table, ctx.kv_len, ctx.buffer, num_heads=num_heads,
                                 num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window,
                                 softcap=softcap, sinks=sinks, exact_weights=exact_weights)
-    if tensor_cores:
+    if tensor_cores and not ctx.all_single:
         return attention_prefill(q, out, pages, page_table, ctx.q_start, ctx.kv_len, ctx.max_new,
                                  num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale,
-                                 window=window, softcap=softcap, sinks=sinks, exact_weights=exact_weights)
+                                 window=window, softcap=softcap, sinks=sinks, exact_weights=exact_weights,
+                                 keep_first=keep_first)
     return attention_plain(q, out, pages, page_table, ctx.seq_ids, ctx.positions, num_heads=num_heads,
                            num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window, softcap=softcap,
-                           sinks=sinks)
+                           sinks=sinks, keep_first=keep_first)
 
 
 # --------------------------------------------------------------------------- latent attention
@@ -1063,13 +1084,15 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gain: torch.Tens
                    positions: torch.Tensor, seq_ids: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor,
                    pages: torch.Tensor, *, num_heads: int, nope_dim: int, rope_dim: int, kv_rank: int,
                    latent_out: Optional[torch.Tensor] = None, shared_out: Optional[torch.Tensor] = None,
-                   q_half: Optional[torch.Tensor] = None) -> None:
+                   q_half: Optional[torch.Tensor] = None, q_from: Optional[torch.Tensor] = None) -> None:
     """From the float32 projection ``proj`` [T, F] (queries at column ``q_off``, [H, nope + rope]; latent and
     shared key part at ``kv_off``, [rank + rope]): RMS-norm the latent with ``gain``, rotate the shared key
     part and write both into ``pages`` [num_pages, page_size, rank + rope] at the tokens' positions; rotate the
     queries' rope parts and write the queries to ``q_out`` float32 [T, H, nope + rope]. Optional bfloat16 copies
     that lie together, for a step that forms every head's keys and values outright: ``latent_out`` [T, rank],
-    ``shared_out`` [T, rope], ``q_half`` [T, H * hd] with hd >= nope + rope (heads padded with zeros)."""
+    ``shared_out`` [T, rope], ``q_half`` [T, H * hd] with hd >= nope + rope (heads padded with zeros).
+    ``q_from``: float32 [T, H * (nope + rope)] (may be a column slice): the queries, when they come from a product
+    of their own (queries formed through a latent) instead of from ``proj``."""
     _want(proj, "latent_prepare proj", torch.float32, 2)
     _want(gain, "latent_prepare gain", torch.float32, 1)
     _want(positions, "latent_prepare positions", torch.int32, 1)
@@ -1094,15 +1117,33 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gain: torch.Tens
         q_half_hd = q_half.shape[1] // H
         if q_half.shape[0] != T or q_half.shape[1] != H * q_half_hd or q_half_hd < dn + dr:
             raise KernelError(f"latent_prepare: q_half {tuple(q_half.shape)} for {H} heads of {dn + dr}")
-    freq_ptr, rot, interleaved = rotation.checked("latent_prepare")
-    if interleaved:
-        raise KernelError("latent_prepare: pairs of neighbours are not supported, only (i, i + half)")
+    freq_ptr, rot, interleaved = rotation.checked("latent_prepare", takes_magnitude=True)
+    q_ptr, ldq = None, 0
+    if q_from is not None:
+        q_ptr, ldq = _slice(q_from, "latent_prepare q_from")
+        if q_from.shape != (T, H * (dn + dr)):
+            raise KernelError(f"latent_prepare: queries {tuple(q_from.shape)} for {H} heads of {dn + dr}")
     lib = library("latent_attention")
     _check(lib, lib.lp_latent_prepare(
         proj.data_ptr(), proj.shape[1], int(q_off), int(kv_off), gain.data_ptr(), float(eps), freq_ptr, rot,
         positions.data_ptr(), seq_ids.data_ptr(), page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(),
         pages.data_ptr(), _code(pages, "latent_prepare pages"), T, H, dn, dr, rank, pages.shape[1], _ptr(latent_out),
-        _ptr(shared_out), _ptr(q_half), q_half_hd, _stream()))
+        _ptr(shared_out), _ptr(q_half), q_half_hd, q_ptr, ldq, interleaved, float(rotation.magnitude), _stream()))
+
+
+def latent_query_norm(proj: torch.Tensor, offset: int, gain: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = rms_norm(proj[t, offset:offset + rank]) * gain for the float32 projection ``proj`` [T, F]: the norm of
+    the latent that queries go through. ``out``: [T, rank], float32 or bfloat16."""
+    _want(proj, "latent_query_norm proj", torch.float32, 2)
+    _want(gain, "latent_query_norm gain", torch.float32, 1)
+    _want(out, "latent_query_norm out", ndim=2)
+    rank = gain.numel()
+    if out.shape != (proj.shape[0], rank):
+        raise KernelError(f"latent_query_norm: out {tuple(out.shape)} for {proj.shape[0]} tokens and rank {rank}")
+    lib = library("latent_attention")
+    _check(lib, lib.lp_latent_query_norm(proj.data_ptr(), proj.shape[1], int(offset), rank, gain.data_ptr(), float(eps),
+                                         out.data_ptr(), _code(out, "latent_query_norm out"), proj.shape[0], _stream()))
+    return out
 
 
 def latent_heads_to_pages(kv: torch.Tensor, shared_part: torch.Tensor, positions: torch.Tensor, seq_ids: torch.Tensor,
@@ -1174,10 +1215,12 @@ def latent_shares(batch: int, max_new: int, num_heads: int, table_width: int, pa
 
 
 def latent_attend(q_abs: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor, q_start: torch.Tensor,
-                  kv_len: torch.Tensor, partials: torch.Tensor, *, max_new: int, kv_rank: int, scale: float) -> torch.Tensor:
+                  kv_len: torch.Tensor, partials: torch.Tensor, *, max_new: int, kv_rank: int, scale: float,
+                  window: Optional[int] = None) -> torch.Tensor:
     """Causal softmax attention of the absorbed queries ``q_abs`` float32 [T, H, rank + rope] over the rows of
     ``pages`` [num_pages, page_size, rank + rope]; ``partials`` float32 [T, H, shares, rank + 2] receives each
-    share's unnormalised latent sum, maximum and sum of weights."""
+    share's unnormalised latent sum, maximum and sum of weights. ``window``: a query at position p sees the keys at
+    positions p - window + 1 .. p only."""
     _want(q_abs, "latent_attend q", torch.float32, 3)
     _want(pages, "latent_attend pages", ndim=3)
     _want(page_table, "latent_attend page_table", torch.int32, 2)
@@ -1195,7 +1238,7 @@ def latent_attend(q_abs: torch.Tensor, pages: torch.Tensor, page_table: torch.Te
     _check(lib, lib.lp_latent_attend(q_abs.data_ptr(), pages.data_ptr(), _code(pages, "latent_attend pages"),
                                      page_table.data_ptr(), page_table.shape[1], q_start.data_ptr(), kv_len.data_ptr(),
                                      partials.data_ptr(), B, int(max_new), H, kv_rank, Dk - kv_rank, pages.shape[1],
-                                     float(scale), shares, _stream()))
+                                     float(scale), shares, int(window) if window else 0, _stream()))
     return partials
 
 
@@ -1269,7 +1312,8 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
              slots: torch.Tensor, q_start: torch.Tensor, out: torch.Tensor, *, num_heads: int, key_dim: int,
              value_dim: int, q_scale: float, max_new: int = 0, scratch=None, decay_per_head: bool = False,
              key_gain: Optional[torch.Tensor] = None, ones_column: bool = False,
-             bonus: Optional[torch.Tensor] = None) -> torch.Tensor:
+             bonus: Optional[torch.Tensor] = None, qk_heads: Optional[int] = None,
+             delta_strength: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The recurrence S <- diag(decay_t) S + k_t v_t^T, out_t = S^T (q_t * q_scale) over the step's tokens of every
     sequence, from and into ``state`` float32 [slots, H, dv, dk] (row ``slots[b]`` for sequence b; a value column's
     key channels lie together). ``proj``: float32
@@ -1283,7 +1327,11 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
     ``value_dim`` columns of state and output is fed the constant 1 instead of a value (the projection then holds
     ``value_dim - 1`` values per head): its output is q . (decayed sum of the gated keys), a normaliser.
     ``bonus``: float32 [H, dk]; a token's output then comes from the state BEFORE the token plus bonus_c k_c v_j for the
-    token itself, out_t = (S + diag(bonus) k_t v_t^T)^T q_t, and the state is updated afterwards."""
+    token itself, out_t = (S + diag(bonus) k_t v_t^T)^T q_t, and the state is updated afterwards.
+    ``qk_heads``: the projection holds that many query / key heads (a divisor of ``num_heads``); head h reads query / key
+    head h // (num_heads // qk_heads). ``delta_strength``: float32 [T, H]; the recurrence is then the gated delta rule
+    (one decay a per head): S <- a S; u = strength * (v - S^T k); S <- S + k u^T; out = S^T q, in one pass over the
+    tokens (no chunks side by side)."""
     _want(proj, "gla_scan proj", torch.float32, 2)
     _want(decay, "gla_scan decay", torch.float32, 2)
     _want(state, "gla_scan state", torch.float32, 4)
@@ -1305,6 +1353,14 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
             or q_start.numel() != B + 1):
         raise KernelError(f"gla_scan: proj {tuple(proj.shape)}, decay {tuple(decay.shape)}, state {tuple(state.shape)}, "
                           f"out {tuple(out.shape)}, {B} sequences")
+    if delta_strength is not None:
+        _want(delta_strength, "gla_scan delta_strength", torch.float32, 2)
+        if delta_strength.shape != (T, H) or not decay_per_head:
+            raise KernelError(f"gla_scan: write strengths {tuple(delta_strength.shape)} for {T} tokens and {H} heads "
+                              f"(the delta rule takes one decay per head)")
+        scratch = None
+    if qk_heads is not None and (qk_heads <= 0 or H % qk_heads):
+        raise KernelError(f"gla_scan: {H} heads over {qk_heads} query / key heads")
     chunks, chunk_state, chunk_decay = 1, None, None
     if scratch is not None and max_new >= GLA_CHUNKED_FROM and B * -(-max_new // GLA_CHUNK) <= 65535:
         chunks = -(-max_new // GLA_CHUNK)
@@ -1314,7 +1370,8 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
     _check(lib, lib.lp_gla_scan(proj.data_ptr(), proj.shape[1], int(q_off), int(k_off), int(v_off), decay.data_ptr(),
                                 state.data_ptr(), slots.data_ptr(), q_start.data_ptr(), out.data_ptr(), B, H, dk, dv,
                                 float(q_scale), chunks, GLA_CHUNK, _ptr(chunk_state), _ptr(chunk_decay),
-                                1 if decay_per_head else 0, _ptr(key_gain), 1 if ones_column else 0, _ptr(bonus), _stream()))
+                                1 if decay_per_head else 0, _ptr(key_gain), 1 if ones_column else 0, _ptr(bonus),
+                                int(qk_heads or H), _ptr(delta_strength), _stream()))
     if chunks > 1:
         count_launches(2)
     return out
@@ -1348,6 +1405,101 @@ def gla_finish(o: torch.Tensor, gain: torch.Tensor, eps: float, gate: Optional[t
     _check(lib, lib.lp_gla_finish(o.data_ptr(), gain.data_ptr(), float(eps), gp, ldg, out.data_ptr(),
                                   _code(out, "gla_finish out"), T, num_heads, value_dim, *_clear_args(clear, "gla_finish"),
                                   xs, 1 if gain_per_head else 0, 1 if gate_sigmoid else 0, _ptr(max_row), _stream()))
+    return out
+
+
+def short_conv(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], tail: torch.Tensor, slots: torch.Tensor,
+               q_start: torch.Tensor, out: torch.Tensor, *, max_new: int, silu: bool = True) -> torch.Tensor:
+    """A short causal convolution over time, per channel, continued from step to step: out[t, c] = act(bias[c] +
+    sum_j taps[c, j] * x[t - (K - 1) + j, c]), the last tap on the token itself, zeros before a sequence's start.
+    ``x``: float32 [T, C] (may be a column slice); ``taps``: [C, K]; ``tail``: float32 [slots, K - 1, C], the last
+    K - 1 inputs of every sequence (zero at its start), read and renewed here; ``out``: float32 [T, C] (may be a slice)."""
+    xp, ldx = _slice(x, "short_conv x")
+    op, ldo = _slice(out, "short_conv out")
+    _want(taps, "short_conv taps", ndim=2)
+    _want(tail, "short_conv tail", torch.float32, 3)
+    _want(slots, "short_conv slots", torch.int32, 1)
+    _want(q_start, "short_conv q_start", torch.int32, 1)
+    T, C = x.shape
+    K = taps.shape[1]
+    B = slots.numel()
+    if taps.shape[0] != C or out.shape != x.shape or tail.shape[1:] != (K - 1, C) or q_start.numel() != B + 1:
+        raise KernelError(f"short_conv: x {tuple(x.shape)}, taps {tuple(taps.shape)}, tail {tuple(tail.shape)}, out "
+                          f"{tuple(out.shape)}, {B} sequences")
+    if bias is not None:
+        _want(bias, "short_conv bias", torch.float32, 1)
+        if bias.numel() != C:
+            raise KernelError(f"short_conv: a bias of {bias.numel()} values for {C} channels")
+    lib = library("linear_attention")
+    _check(lib, lib.lp_short_conv(xp, ldx, taps.data_ptr(), _code(taps, "short_conv taps"), _ptr(bias), tail.data_ptr(),
+                                  slots.data_ptr(), q_start.data_ptr(), op, ldo, B, int(max_new), C, K, 1 if silu else 0,
+                                  _stream()))
+    return out
+
+
+def decay_gates(proj: torch.Tensor, z_off: int, dt_bias: Optional[torch.Tensor], a_log: torch.Tensor, decay: torch.Tensor,
+                dt: Optional[torch.Tensor] = None, strength: Optional[torch.Tensor] = None, b_off: int = 0) -> None:
+    """Per token and head, from float32 columns of ``proj``: step = softplus(proj[:, z_off + h] + dt_bias[h]) (no
+    clamp), decay = exp(-exp(a_log[h]) * step); optionally strength = sigmoid(proj[:, b_off + h]). ``decay``, ``dt``,
+    ``strength``: float32 [T, H]."""
+    _want(proj, "decay_gates proj", torch.float32, 2)
+    _want(a_log, "decay_gates a_log", torch.float32, 1)
+    _want(decay, "decay_gates decay", torch.float32, 2)
+    T, H = decay.shape
+    if proj.shape[0] != T or a_log.numel() != H:
+        raise KernelError(f"decay_gates: proj {tuple(proj.shape)}, decay {tuple(decay.shape)}, {a_log.numel()} heads")
+    for name, t in (("dt", dt), ("strength", strength)):
+        if t is not None:
+            _want(t, f"decay_gates {name}", torch.float32, 2)
+            if t.shape != decay.shape:
+                raise KernelError(f"decay_gates: {name} {tuple(t.shape)} for {tuple(decay.shape)}")
+    if dt_bias is not None:
+        _want(dt_bias, "decay_gates dt_bias", torch.float32, 1)
+        if dt_bias.numel() != H:
+            raise KernelError(f"decay_gates: {dt_bias.numel()} biases for {H} heads")
+    lib = library("linear_attention")
+    _check(lib, lib.lp_decay_gates(proj.data_ptr(), proj.shape[1], int(z_off), int(b_off), _ptr(dt_bias), a_log.data_ptr(),
+                                   decay.data_ptr(), _ptr(dt), _ptr(strength), T, H, _stream()))
+
+
+def head_unit_norm(x: torch.Tensor, offset: int, heads: int, dim: int, eps: float, scale: float = 1.0,
+                   scaled_heads: Optional[int] = None) -> torch.Tensor:
+    """In place, for ``heads`` heads of ``dim`` values from column ``offset`` of the float32 matrix ``x``: every head
+    becomes x / sqrt(sum(x^2) + eps); the first ``scaled_heads`` of them (all, if None) are also multiplied by ``scale``."""
+    _want(x, "head_unit_norm x", torch.float32, 2)
+    lib = library("linear_attention")
+    _check(lib, lib.lp_head_unit_norm(x.data_ptr(), x.shape[1], int(offset), int(heads), int(dim), float(eps), float(scale),
+                                      int(heads if scaled_heads is None else scaled_heads), x.shape[0], _stream()))
+    return x
+
+
+def gated_part_norm(raw: torch.Tensor, gate: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor, *,
+                    num_heads: int, head_dim: int, parts: int, values: Optional[torch.Tensor] = None,
+                    skip: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = (raw + skip[h] * values) * silu(gate), then each of ``parts`` equal parts of a row is divided by its own root
+    mean square (``eps`` inside the root) and multiplied by ``gain``. ``raw``: float32 [T, H * P]; ``gate`` and ``values``:
+    float32 [T, H * P] (may be column slices); ``skip``: float32 [H]; ``gain``: float32 [H * P]. The gate comes before the
+    norm. ``clear``: a float32 buffer zeroed on the side."""
+    _want(raw, "gated_part_norm raw", torch.float32, 2)
+    _want(gain, "gated_part_norm gain", torch.float32, 1)
+    _want(out, "gated_part_norm out", ndim=2)
+    T, W = raw.shape
+    gp, ldg = _slice(gate, "gated_part_norm gate")
+    if W != num_heads * head_dim or gate.shape != raw.shape or out.shape != raw.shape or gain.numel() != W or parts <= 0 or W % parts:
+        raise KernelError(f"gated_part_norm: raw {tuple(raw.shape)}, gate {tuple(gate.shape)}, out {tuple(out.shape)}, "
+                          f"{num_heads} heads of {head_dim} in {parts} parts")
+    vp, ldv = None, 0
+    if (values is None) != (skip is None):
+        raise KernelError("gated_part_norm: a skip comes with the values it multiplies")
+    if values is not None:
+        vp, ldv = _slice(values, "gated_part_norm values")
+        _want(skip, "gated_part_norm skip", torch.float32, 1)
+        if values.shape != raw.shape or skip.numel() != num_heads:
+            raise KernelError(f"gated_part_norm: values {tuple(values.shape)}, {skip.numel()} skips for {num_heads} heads")
+    lib = library("linear_attention")
+    _check(lib, lib.lp_gated_part_norm(raw.data_ptr(), vp, ldv, _ptr(skip), gp, ldg, gain.data_ptr(), float(eps), out.data_ptr(),
+                                       _code(out, "gated_part_norm out"), T, num_heads, head_dim, int(parts),
+                                       *_clear_args(clear, "gated_part_norm"), _stream()))
     return out
 
 
@@ -1538,6 +1690,27 @@ def stream_add(x: torch.Tensor, other: Optional[torch.Tensor] = None, vector: Op
     return x
 
 
+def scaled_sum(x: torch.Tensor, a: torch.Tensor, a_scale: float, b: Optional[torch.Tensor] = None, b_scale: float = 0.0, *,
+               a_vector: Optional[torch.Tensor] = None, b_vector: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x <- x + a_scale * (a + a_vector) + b_scale * (b + b_vector), float32 [T, d] in place; the vectors [d] and ``b``
+    are optional."""
+    _want(x, "scaled_sum x", torch.float32, 2)
+    for name, t in (("a", a), ("b", b)):
+        if t is not None:
+            _want(t, f"scaled_sum {name}", torch.float32, 2)
+            if t.shape != x.shape:
+                raise KernelError(f"scaled_sum: {name} {tuple(t.shape)} does not match x {tuple(x.shape)}")
+    for name, t in (("a_vector", a_vector), ("b_vector", b_vector)):
+        if t is not None:
+            _want(t, f"scaled_sum {name}", torch.float32, 1)
+            if t.numel() != x.shape[1]:
+                raise KernelError(f"scaled_sum: {name} of {t.numel()} values for rows of {x.shape[1]}")
+    lib = library("elementwise")
+    _check(lib, lib.lp_scaled_sum(x.data_ptr(), a.data_ptr(), _ptr(a_vector), float(a_scale), _ptr(b), _ptr(b_vector),
+                                  float(b_scale), x.shape[0], x.shape[1], _stream()))
+    return x
+
+
 def relu2(z: torch.Tensor, out: torch.Tensor, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = max(z, 0)^2; ``z``: float32 [T, F] (may be a column slice)."""
     zp, ldz = _slice(z, "relu2 z")
@@ -1566,17 +1739,55 @@ def route(logits: torch.Tensor, weights: torch.Tensor, *, groups: int, keep: int
     return weights
 
 
-def expert_scale(hidden: torch.Tensor, weights: torch.Tensor, expert_size: int, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """hidden[t, e * expert_size + j] *= weights[t, e] in place for the E experts of ``weights`` [T, E]; columns of
-    ``hidden`` beyond E * expert_size are left as they are."""
+def route_softmax(logits: torch.Tensor, correction: Optional[torch.Tensor], weights: torch.Tensor, *, groups: int, keep: int,
+                  top: int, scale: float) -> torch.Tensor:
+    """Scores softmax(logits) over all E router outputs; the choice is made on score + correction inside the best
+    ``keep`` of ``groups`` groups of neighbours (a group's score is its largest choice score), the ``top`` largest win;
+    weights[t, e] = score * ``scale`` for the chosen, zero otherwise (not renormalised). ``logits``: float32 [T, E] (may
+    be a column slice); ``correction``: float32 [E] or None; ``weights``: float32 [T, E]."""
+    zp, ldz = _slice(logits, "route_softmax logits")
+    _want(weights, "route_softmax weights", torch.float32, 2)
+    T, E = logits.shape
+    if weights.shape != (T, E):
+        raise KernelError(f"route_softmax: logits {tuple(logits.shape)}, weights {tuple(weights.shape)}")
+    if correction is not None:
+        _want(correction, "route_softmax correction", torch.float32, 1)
+        if correction.numel() != E:
+            raise KernelError(f"route_softmax: a correction of {correction.numel()} values for {E} experts")
+    lib = library("routing")
+    _check(lib, lib.lp_route_softmax(zp, ldz, _ptr(correction), weights.data_ptr(), weights.shape[1], T, E, int(groups),
+                                     int(keep), int(top), float(scale), _stream()))
+    return weights
+
+
+def identity_experts(x: torch.Tensor, h: torch.Tensor, weights: torch.Tensor, first: int, count: int) -> torch.Tensor:
+    """x[t] += h[t] * sum(weights[t, first:first + count]): experts that pass their input on. ``x``: float32 [T, d];
+    ``h``: [T, d]; ``weights``: float32 [T, E]."""
+    _want(x, "identity_experts x", torch.float32, 2)
+    _want(h, "identity_experts h", ndim=2)
+    _want(weights, "identity_experts weights", torch.float32, 2)
+    if h.shape != x.shape or weights.shape[0] != x.shape[0] or first < 0 or first + count > weights.shape[1]:
+        raise KernelError(f"identity_experts: x {tuple(x.shape)}, h {tuple(h.shape)}, weights {tuple(weights.shape)}, "
+                          f"columns {first}..{first + count - 1}")
+    lib = library("routing")
+    _check(lib, lib.lp_identity_experts(x.data_ptr(), h.data_ptr(), _code(h, "identity_experts h"), weights.data_ptr(),
+                                        weights.shape[1], int(first), int(count), x.shape[0], x.shape[1], _stream()))
+    return x
+
+
+def expert_scale(hidden: torch.Tensor, weights: torch.Tensor, expert_size: int, clear: Optional[torch.Tensor] = None,
+                 num_experts: Optional[int] = None) -> torch.Tensor:
+    """hidden[t, e * expert_size + j] *= weights[t, e] in place for the E experts of ``weights`` [T, E] (``num_experts``:
+    for its first so many columns only); columns of ``hidden`` beyond E * expert_size are left as they are."""
     _want(hidden, "expert_scale hidden", ndim=2)
     _want(weights, "expert_scale weights", torch.float32, 2)
-    T, E = weights.shape
-    if hidden.shape[0] != T or hidden.shape[1] < E * expert_size:
+    T, ldw = weights.shape
+    E = ldw if num_experts is None else int(num_experts)
+    if hidden.shape[0] != T or hidden.shape[1] < E * expert_size or not 0 < E <= ldw:
         raise KernelError(f"expert_scale: hidden {tuple(hidden.shape)} for {E} experts of {expert_size}")
     lib = library("routing")
     _check(lib, lib.lp_expert_scale(hidden.data_ptr(), _code(hidden, "expert_scale hidden"), hidden.shape[1],
-                                    weights.data_ptr(), E, T, E, int(expert_size), *_clear_args(clear, "expert_scale"), _stream()))
+                                    weights.data_ptr(), ldw, T, E, int(expert_size), *_clear_args(clear, "expert_scale"), _stream()))
     return hidden
 
 

@@ -38,6 +38,10 @@ class Attention(Part):
             raise ConfigError("a learned sink per head and a constant sink exclude each other")
         if s.shares_kv and (s.k_bias is not None or s.v_bias is not None or s.k_norm is not None):
             raise ConfigError("a layer that attends over another layer's keys and values has no key or value tensors")
+        if s.keep_first is not None and (s.keep_first < 0 or (s.keep_first > 0 and s.window is None)):
+            raise ConfigError(f"first tokens kept beyond a window need a window (keep_first {s.keep_first}, window {s.window})")
+        if s.keep_first and s.shares_kv:
+            raise ConfigError("a layer that attends over another layer's keys and values keeps no first tokens of its own")
         if s.softcap is not None and not s.softcap > 0:
             raise ConfigError(f"score cap must be positive or absent, got {s.softcap}")
         self.spec = spec
@@ -113,7 +117,8 @@ class Attention(Part):
         s = self.spec
         if s.shares_kv:
             return None
-        return KVRequest(s.num_kv_heads, self.stored_dim, s.window if s.cache_window == "own" else s.cache_window)
+        return KVRequest(s.num_kv_heads, self.stored_dim, s.window if s.cache_window == "own" else s.cache_window,
+                         int(s.keep_first or 0))
 
     # ------------------------------------------------------------------ step
     def buffer_to_clear(self, ctx, tokens: int):
@@ -173,7 +178,8 @@ class Attention(Part):
         o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
         with ops.section("attention.scores"):
             ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd, scale=s.scale,
-                          window=s.window, fast=rt.fast, softcap=s.softcap, sinks=self.sinks, exact_weights=s.exact_weights)
+                          window=s.window, fast=rt.fast, softcap=s.softcap, sinks=self.sinks, exact_weights=s.exact_weights,
+                          keep_first=int(s.keep_first or 0))
         with ops.section("attention.out"):
             if overwrite:
                 if clear is not None:

@@ -25,14 +25,16 @@ class PreNormBlock(Part):
         self.spec = spec
         self.mixer_norm = NORMS.build(spec.mixer_norm)
         self.mixer = MIXERS.build(spec.mixer)
-        self.ffn_norm = NORMS.build(spec.ffn_norm)
-        self.ffn = FEED_FORWARDS.build(spec.ffn)
+        if (spec.ffn is None) != (spec.ffn_norm is None):
+            raise ConfigError("a feed-forward comes with the norm in front of it, or not at all")
+        self.ffn_norm = NORMS.build(spec.ffn_norm) if spec.ffn is not None else None
+        self.ffn = FEED_FORWARDS.build(spec.ffn) if spec.ffn is not None else None
         # parts may offer to write the norm that follows them (a `then_norm` argument of forward)
-        self._mixer_fuses = "then_norm" in inspect.signature(self.mixer.forward).parameters
-        self._ffn_fuses = "then_norm" in inspect.signature(self.ffn.forward).parameters
+        self._mixer_fuses = self.ffn is not None and "then_norm" in inspect.signature(self.mixer.forward).parameters
+        self._ffn_fuses = self.ffn is not None and "then_norm" in inspect.signature(self.ffn.forward).parameters
 
     def children(self):
-        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
 
     @property
     def capture_safe(self) -> bool:
@@ -79,6 +81,9 @@ class PreNormBlock(Part):
         else:
             self._norm(ctx, self.mixer_norm, self.mixer, residual, h)
             mixer_in = h
+        if self.ffn is None:                 # a layer without a feed-forward
+            self.mixer.forward(ctx, cache, mixer_in, residual)
+            return False
         fused = False
         if self._mixer_fuses and not ffn_pends:
             follow = FollowingNorm(self.ffn_norm, h, self._clear_for(ctx, self.ffn, tokens))

@@ -53,6 +53,9 @@ class LinearHead(Part):
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         super().load(tensors, runtime)
         self.norm.load(tensors, runtime)
+        if self.spec.logit_scale != 1.0:
+            # logits = head(norm(x)) * c = head(norm(x) * c): the constant rides on the norm's float32 gain
+            self.norm.weight = self.norm.weight * float(self.spec.logit_scale)
         self.proj = Linear([tensors[self.spec.weight]], runtime)
 
     def forward(self, ctx, residual: torch.Tensor, rows: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:

@@ -272,8 +272,15 @@ class Mixture(Part):
 
     def __init__(self, spec: MixtureSpec):
         s, r = spec, spec.routing
-        if r.scoring not in ("sigmoid_groups", "softmax_top"):
+        if r.scoring not in ("sigmoid_groups", "softmax_top", "softmax_groups"):
             raise ConfigError(f"unknown scoring {r.scoring!r} of a router")
+        if r.scoring != "softmax_groups" and (r.correction is not None or r.identity_experts or r.weight_scale != 1.0):
+            raise ConfigError("a correction of the choice, identity experts and a constant on the weights belong to "
+                              "scoring 'softmax_groups'")
+        if r.identity_experts < 0:
+            raise ConfigError(f"{r.identity_experts} identity experts")
+        if r.scoring == "softmax_groups" and (s.shared_size > 0 or s.activation != "silu"):
+            raise ConfigError("scoring 'softmax_groups' comes with silu experts and without a shared expert")
         if s.activation not in ("silu", "clamped"):
             raise ConfigError(f"unknown activation {s.activation!r} of the experts")
         if s.activation == "clamped" and (not s.limit > 0 or (s.shared_size > 0 and not s.shared_limit > 0)):
@@ -286,12 +293,13 @@ class Mixture(Part):
             raise ConfigError("the shared expert of clamped experts comes with its gate")
         if s.shared_gate is not None and (s.shared_size <= 0 or r.scoring != "softmax_top" or s.activation != "clamped"):
             raise ConfigError("a gate of the shared expert belongs to clamped experts chosen by their largest logits")
-        if r.num_experts <= 0 or r.groups <= 0 or r.num_experts % r.groups:
-            raise ConfigError(f"{r.num_experts} experts cannot form {r.groups} equal groups")
+        outputs = r.num_experts + r.identity_experts          # groups are formed over experts and identity experts together
+        if r.num_experts <= 0 or r.groups <= 0 or outputs % r.groups:
+            raise ConfigError(f"{outputs} experts cannot form {r.groups} equal groups")
         if not 0 < r.keep_groups <= r.groups:
             raise ConfigError(f"{r.keep_groups} of {r.groups} groups kept")
-        if not 0 < r.top <= r.keep_groups * (r.num_experts // r.groups):
-            raise ConfigError(f"{r.top} experts cannot be chosen from {r.keep_groups} groups of {r.num_experts // r.groups}")
+        if not 0 < r.top <= r.keep_groups * (outputs // r.groups):
+            raise ConfigError(f"{r.top} experts cannot be chosen from {r.keep_groups} groups of {outputs // r.groups}")
         if s.expert_size <= 0 or s.shared_size < 0 or (s.shared_size > 0 and not s.shared_prefix):
             raise ConfigError(f"experts of {s.expert_size}, a shared expert of {s.shared_size}")
         self.spec = spec
@@ -313,7 +321,9 @@ class Mixture(Part):
             out[prefix + "gate"] = TensorSpec((size, s.hidden_size), MATRIX)
             out[prefix + "up"] = TensorSpec((size, s.hidden_size), MATRIX)
             out[prefix + "down"] = TensorSpec((s.hidden_size, size), MATRIX)
-        out[s.routing.router] = TensorSpec((s.routing.num_experts, s.hidden_size), MATRIX)
+        out[s.routing.router] = TensorSpec((s.routing.num_experts + s.routing.identity_experts, s.hidden_size), MATRIX)
+        if s.routing.correction is not None:
+            out[s.routing.correction] = TensorSpec((s.routing.num_experts + s.routing.identity_experts,), BIAS)
         if s.routing.router_bias is not None:
             out[s.routing.router_bias] = TensorSpec((s.routing.num_experts,), BIAS)
         if s.shared_gate is not None:
@@ -332,6 +342,7 @@ class Mixture(Part):
         self.router = Linear([tensors[s.routing.router]] + ([tensors[s.shared_gate]] if s.shared_gate is not None else []),
                              runtime)
         self.router_bias = runtime.gain(tensors[s.routing.router_bias]) if s.routing.router_bias is not None else None
+        self.correction = runtime.gain(tensors[s.routing.correction]) if s.routing.correction is not None else None
         # silu experts: the gated product applies the activation itself; clamped ones: float32 sums, then a kernel
         self.gate_up = Linear([gate, up], runtime, gated=s.activation == "silu")
         self.down = Linear([down], runtime)
@@ -354,6 +365,9 @@ class Mixture(Part):
             weights = ctx.buffer("router_weights", (T, columns), torch.float32)
             if r.scoring == "softmax_top":
                 ops.route_top(logits, self.router_bias, weights, num_experts=r.num_experts, top=r.top)
+            elif r.scoring == "softmax_groups":
+                ops.route_softmax(logits, self.correction, weights, groups=r.groups, keep=r.keep_groups, top=r.top,
+                                  scale=r.weight_scale)
             else:
                 ops.route(logits, weights, groups=r.groups, keep=r.keep_groups, top=r.top)
         h = ctx.buffer("ffn_hidden", (T, self.total), self.runtime.act_dtype)
@@ -369,7 +383,7 @@ class Mixture(Part):
             with ops.section("ffn.gate_up"):
                 self.gate_up.swiglu(x, h, ctx)
             with ops.section("ffn.weights"):
-                ops.expert_scale(h, weights, s.expert_size, clear=clear)
+                ops.expert_scale(h, weights, s.expert_size, clear=clear, num_experts=r.num_experts)
         with ops.section("ffn.down"):
             if clear is not None:
                 ctx.note_cleared()
@@ -377,6 +391,10 @@ class Mixture(Part):
                 self.down.store(h, residual, ctx)
             else:
                 self.down.accumulate(h, residual, ctx)
+        if r.identity_experts:
+            # experts that are the identity: the feed-forward's input itself, times the token's weights for them
+            with ops.section("ffn.identity"):
+                ops.identity_experts(residual, x, weights, r.num_experts, r.identity_experts)
         return False
 
 

@@ -34,6 +34,10 @@ class LatentAttention(Part):
             raise ConfigError(f"latent attention with {s.num_heads} heads, rank {s.kv_rank}, values of {s.value_dim}")
         if s.nope_dim < 0 or s.rope_dim < 0 or s.nope_dim + s.rope_dim <= 0:
             raise ConfigError(f"latent attention: query heads of {s.nope_dim} + {s.rope_dim}")
+        if (s.q_down is None) != (s.q_norm is None) or (s.q_down is not None and s.q_rank <= 0):
+            raise ConfigError("queries through a latent need its map, its norm's gain and its rank together")
+        if s.window is not None and s.window <= 0:
+            raise ConfigError(f"attention window must be positive or absent, got {s.window}")
         self.spec = spec
         self.position = POSITIONS.build(s.position)
         self._inputs: List[torch.Tensor] = []
@@ -48,7 +52,7 @@ class LatentAttention(Part):
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         s = self.spec
         specs = {
-            s.q: TensorSpec((s.num_heads * (s.nope_dim + s.rope_dim), s.hidden_size), MATRIX),
+            s.q: TensorSpec((s.num_heads * (s.nope_dim + s.rope_dim), s.q_rank if s.q_down is not None else s.hidden_size), MATRIX),
             s.kv_down: TensorSpec((s.kv_rank + s.rope_dim, s.hidden_size), MATRIX),
             s.latent_norm: TensorSpec((s.kv_rank,), GAIN),
             s.k_up: TensorSpec((s.num_heads * s.nope_dim, s.kv_rank), MATRIX),
@@ -56,13 +60,21 @@ class LatentAttention(Part):
         }
         if s.out_gate is not None:
             specs[s.out_gate] = TensorSpec((s.num_heads, s.hidden_size), MATRIX)
+        if s.q_down is not None:
+            specs[s.q_down] = TensorSpec((s.q_rank, s.hidden_size), MATRIX)
+            specs[s.q_norm] = TensorSpec((s.q_rank,), GAIN)
         specs[s.o] = TensorSpec((s.hidden_size, s.num_heads * s.value_dim), MATRIX)
         return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         super().load(tensors, runtime)
         s = self.spec
-        self._inputs = [tensors[s.q], tensors[s.kv_down]] + ([tensors[s.out_gate]] if s.out_gate is not None else [])
+        # what multiplies the mixer's input: the queries' map (or, where queries go through a latent, that latent's
+        # map, in the same place), the latent's map, the output gate
+        self._inputs = ([tensors[s.q_down] if s.q_down is not None else tensors[s.q], tensors[s.kv_down]]
+                        + ([tensors[s.out_gate]] if s.out_gate is not None else []))
+        self.q_up = Linear([tensors[s.q]], runtime) if s.q_down is not None else None
+        self.q_gain = runtime.gain(tensors[s.q_norm]) if s.q_down is not None else None
         self.k_up = runtime.matrix(tensors[s.k_up])
         self.v_up = runtime.matrix(tensors[s.v_up])
         self._k_up_host, self._v_up_host = tensors[s.k_up], tensors[s.v_up]
@@ -74,7 +86,7 @@ class LatentAttention(Part):
 
     # ------------------------------------------------------------------ cache
     def cache_request(self):
-        return RowsRequest(self.spec.kv_rank + self.spec.rope_dim)
+        return RowsRequest(self.spec.kv_rank + self.spec.rope_dim, self.spec.window)
 
     # ------------------------------------------------------------------ step
     def input_projections(self) -> List[torch.Tensor]:
@@ -90,26 +102,36 @@ class LatentAttention(Part):
         T = proj.shape[0]
         H, dn, dr, dv, rank = s.num_heads, s.nope_dim, s.rope_dim, s.value_dim, s.kv_rank
         q_off = offset
-        kv_off = q_off + H * (dn + dr)
+        kv_off = q_off + (s.q_rank if s.q_down is not None else H * (dn + dr))
         gate_off = kv_off + rank + dr
         rotation = self.position.rotation()
         if rotation is None:
             raise ConfigError("latent attention takes position encodings that are rotations")
         table = ctx.page_tables[cache.group_index]
+        q_from = None
+        if s.q_down is not None:
+            # queries through their own latent: its RMS norm (float32), then the queries' map
+            with ops.section("attention.qkv"):
+                q_latent = ctx.buffer("latent_q_latent", (T, s.q_rank), rt.act_dtype)
+                ops.latent_query_norm(proj, q_off, self.q_gain, s.norm_eps, q_latent)
+                q_from = ctx.buffer("latent_q_proj", (T, H * (dn + dr)), torch.float32)
+                self.q_up.store(q_latent, q_from, ctx)
         q = ctx.buffer("latent_q", (T, H, dn + dr), torch.float32)
         if self._forms_heads(ctx, cache):
-            return self._forward_heads(ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out)
+            return self._forward_heads(ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out, q_from)
         with ops.section("attention.position"):
             ops.latent_prepare(proj, q_off, kv_off, self.latent_gain, s.norm_eps, rotation, ctx.positions, ctx.seq_ids,
-                               table, q, cache.pages, num_heads=H, nope_dim=dn, rope_dim=dr, kv_rank=rank)
+                               table, q, cache.pages, num_heads=H, nope_dim=dn, rope_dim=dr, kv_rank=rank, q_from=q_from)
         q_abs = ctx.buffer("latent_q_absorbed", (T, H, rank + dr), torch.float32)
         with ops.section("attention.absorb"):
             ops.latent_absorb(q, self.k_up, q_abs, nope_dim=dn, rope_dim=dr)
         shares = ops.latent_shares(ctx.num_sequences, ctx.max_new, H, table.shape[1], cache.pages.shape[1])
+        if s.window is not None:
+            shares = min(shares, -(-s.window // 32) + 1)        # a row sees that many blocks of 32 keys at most
         partials = ctx.buffer("latent_partials", (T, H, shares, rank + 2), torch.float32)
         with ops.section("attention.scores"):
             ops.latent_attend(q_abs, cache.pages, table, ctx.q_start, ctx.kv_len, partials, max_new=ctx.max_new,
-                              kv_rank=rank, scale=s.scale)
+                              kv_rank=rank, scale=s.scale, window=s.window)
         o = ctx.buffer("attn_out", (T, H * dv), rt.act_dtype)
         gate = proj[:, gate_off:gate_off + H] if s.out_gate is not None else None
         clear = self._out_to_clear(ctx, T, out)
@@ -151,7 +173,7 @@ class LatentAttention(Part):
         need = self.spec.nope_dim + self.spec.rope_dim
         return next((size for size in (64, 128, 192, 256) if need <= size), None)
 
-    def _forward_heads(self, ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out):
+    def _forward_heads(self, ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out, q_from=None):
         s = self.spec
         T = proj.shape[0]
         H, dn, dr, dv, rank = s.num_heads, s.nope_dim, s.rope_dim, s.value_dim, s.kv_rank
@@ -163,7 +185,7 @@ class LatentAttention(Part):
         with ops.section("attention.position"):
             ops.latent_prepare(proj, q_off, kv_off, self.latent_gain, s.norm_eps, rotation, ctx.positions, ctx.seq_ids,
                                table, q, cache.pages, num_heads=H, nope_dim=dn, rope_dim=dr, kv_rank=rank,
-                               latent_out=latent, shared_out=shared, q_half=q_half)
+                               latent_out=latent, shared_out=shared, q_half=q_half, q_from=q_from)
         if self._up is None:
             self._up = Linear([self._k_up_host, self._v_up_host], self.runtime)
         kv = ctx.buffer("latent_heads", (T, H * (dn + dv)), torch.bfloat16)
@@ -184,7 +206,8 @@ class LatentAttention(Part):
         heads = ctx.buffer("latent_head_out", (T, H * hd), torch.bfloat16)
         with ops.section("attention.scores"):
             ops.attention_prefill(q_half, heads, step_pages, step_table, ctx.q_start, ctx.kv_len, ctx.max_new, num_heads=H,
-                                  num_kv_heads=H, head_dim=hd, scale=s.scale, window=None)
+                                  num_kv_heads=H, head_dim=hd, scale=s.scale, window=s.window,
+                                  exact_weights=s.exact_weights)
         o = ctx.buffer("attn_out", (T, H * dv), torch.bfloat16)
         gate = proj[:, gate_off:gate_off + H] if s.out_gate is not None else None
         clear = self._out_to_clear(ctx, T, out)
@@ -195,6 +218,11 @@ class LatentAttention(Part):
         with ops.section("attention.out"):
             self.out.store(o, out, ctx)
         return out
+
+    def buffer_to_clear(self, ctx, tokens: int):
+        if self._own is None:
+            self._own = Linear(self._inputs, self.runtime)
+        return self._own.sums_into(ctx, tokens, "mixer_proj", ops.STORE)
 
     def forward(self, ctx, cache, x, residual: torch.Tensor) -> bool:
         """Adds the mixer's output into ``residual`` (for blocks that hand over a normed input only)."""

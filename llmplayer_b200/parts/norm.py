@@ -55,9 +55,9 @@ class LayerNorm(Part):
 
     def apply(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
               add: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if add is not None or clear is not None:
-            raise ConfigError("the layer norm kernel neither adds a residual nor clears a buffer on the side")
-        return ops.layernorm(x, self.weight, self.spec.eps, out, rows=rows)
+        if add is not None:
+            raise ConfigError("the layer norm kernel does not add a residual on the way")
+        return ops.layernorm(x, self.weight, self.spec.eps, out, rows=rows, clear=clear)
 
 
 NORMS.register("rmsnorm", RMSNorm)

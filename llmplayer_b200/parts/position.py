@@ -26,7 +26,7 @@ import torch
 from ..errors import ConfigError
 from ..kernels import ops
 from .base import POSITIONS, Part, Runtime
-from .specs import PositionSpec
+from .specs import Llama3Scaling, PositionSpec, YarnScaling
 
 
 def inverse_frequencies(spec: PositionSpec) -> torch.Tensor:
@@ -36,9 +36,23 @@ def inverse_frequencies(spec: PositionSpec) -> torch.Tensor:
         raise ConfigError(f"rope theta must be positive, got {spec.theta}")
     freqs = []
     s = spec.scaling
+    if s is not None and not isinstance(s, (Llama3Scaling, YarnScaling)):
+        raise ConfigError(f"unknown scaling of rotary frequencies: {s!r}")
+    lo = hi = 0
+    if isinstance(s, YarnScaling):
+        if not s.factor > 0 or s.original <= 0 or not s.fast > 0 or not s.slow > 0 or spec.theta == 1.0:
+            raise ConfigError(f"rotary scaling needs positive factor, original, fast and slow and a base other than 1: {s!r}")
+        # the pair that makes t turns over the original context, as a (fractional) pair index
+        def turn(t: float) -> float:
+            return spec.rotary_dim * math.log(s.original / (2.0 * math.pi * t)) / (2.0 * math.log(spec.theta))
+        lo = max(math.floor(turn(s.fast)), 0)
+        hi = min(math.ceil(turn(s.slow)), spec.rotary_dim - 1)
     for i in range(spec.rotary_dim // 2):
         f = 1.0 / math.pow(spec.theta, 2.0 * i / spec.rotary_dim)
-        if s is not None:
+        if isinstance(s, YarnScaling):
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            f = f / s.factor * ramp + f * (1.0 - ramp)
+        elif s is not None:
             wavelength = 2.0 * math.pi / f
             short = s.original_max_position / s.high_freq_factor
             long = s.original_max_position / s.low_freq_factor
@@ -50,6 +64,13 @@ def inverse_frequencies(spec: PositionSpec) -> torch.Tensor:
                 f = (1.0 - blend) * f / s.factor + blend * f
         freqs.append(f)
     return torch.tensor(freqs, dtype=torch.float64).to(torch.float32)
+
+
+def rotation_magnitude(spec: PositionSpec) -> float:
+    """The factor on both cosine and sine that a scaling rule brings along (one where it brings none)."""
+    if isinstance(spec.scaling, YarnScaling):
+        return 0.1 * math.log(spec.scaling.factor) + 1.0
+    return 1.0
 
 
 class Rotary(Part):
@@ -66,7 +87,8 @@ class Rotary(Part):
         super().load(tensors, runtime)
         # layers with equal specifications share one table of frequencies (and, per step, one table of angles)
         inv_freq = runtime.shared(("rotary", self.spec), lambda: inverse_frequencies(self.spec).to(runtime.device))
-        self._rotation = ops.Rotation(inv_freq, self.spec.rotary_dim, self.spec.pairing == "interleaved")
+        self._rotation = ops.Rotation(inv_freq, self.spec.rotary_dim, self.spec.pairing == "interleaved",
+                                      rotation_magnitude(self.spec))
 
     def rotation(self) -> Optional[ops.Rotation]:
         return self._rotation

@@ -61,18 +61,31 @@ class Llama3Scaling:
 
 
 @dataclass(frozen=True)
+class YarnScaling:
+    """Stretching of rotary frequencies by how many turns a pair makes over the ``original`` context ("YaRN"). With
+    turn(t) = dims * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(turn(fast)), 0), hi = min(ceil(turn(slow)),
+    dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i rotates by f_i / factor * ramp_i +
+    f_i * (1 - ramp_i), and cosine and sine are both multiplied by 0.1 * ln(factor) + 1."""
+    factor: float
+    original: int
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class PositionSpec:
     """Position encoding applied to queries and keys inside a mixer.
 
     ``kind="rope"`` rotates the first ``rotary_dim`` features of each head;
     ``pairing`` is ``"split_half"`` (feature i with i + rotary_dim/2) or
     ``"interleaved"`` (2i with 2i+1). ``kind="none"`` leaves them as they are.
+    ``scaling``: a :class:`Llama3Scaling` or a :class:`YarnScaling`.
     """
     kind: str = "rope"
     head_dim: int = 0
     rotary_dim: int = 0
     theta: float = 0.0
-    scaling: Optional[Llama3Scaling] = None
+    scaling: Optional[object] = None
     pairing: str = "split_half"
 
 
@@ -114,10 +127,11 @@ class AttentionSpec:
     # The window that the layer's cache must keep (None: everything) when layers that attend over this layer's keys look
     # further back than the layer itself; "own": the layer's own ``window``.
     cache_window: object = "own"
+    keep_first: Optional[int] = None     # with ``window``: a sequence's first so many tokens stay visible to every later query, at their true positions
 
     @property
     def general(self) -> bool:
-        return (self.value_dim not in (None, self.head_dim) or any(b is not None for b in (self.q_bias, self.k_bias, self.v_bias))
+        return (bool(self.keep_first) or self.value_dim not in (None, self.head_dim) or any(b is not None for b in (self.q_bias, self.k_bias, self.v_bias))
                 or self.unit_norm_eps is not None or self.softcap is not None or self.sink is not None or self.exact_weights
                 or self.q_norm is not None or self.k_norm is not None or self.o_bias is not None or self.sink_value is not None)
 
@@ -142,6 +156,9 @@ class LatentAttentionSpec:
     unrotated key is ``k_up`` [h] times the latent, its value ``v_up`` [h] times the latent; a query head is
     laid out [``nope_dim`` unrotated | ``rope_dim`` rotated]. ``position`` rotates the ``rope_dim`` part.
     ``out_gate`` (optional): a matrix [heads, hidden] whose sigmoid scales each head's output.
+    ``q_down`` / ``q_norm`` (optional, together): queries go through a latent of their own, q = ``q`` rms_norm(``q_down`` x)
+    with the gain ``q_norm``; ``q`` is then [heads * (nope + rope), q_rank], the rank read off ``q_down``'s config size
+    ``q_rank``. ``window``: a query at position p sees keys p - window + 1 .. p (None: all earlier keys).
     """
     hidden_size: int
     num_heads: int
@@ -160,6 +177,11 @@ class LatentAttentionSpec:
     o: str
     out_gate: Optional[str] = None
     kind: str = "latent_attention"
+    q_down: Optional[str] = None
+    q_norm: Optional[str] = None
+    q_rank: int = 0
+    window: Optional[int] = None
+    exact_weights: bool = False          # prompts run as ordinary heads: softmax weights meet the values at float32 precision
 
 
 @dataclass(frozen=True)
@@ -217,6 +239,79 @@ class MatrixMemorySpec:
     out_norm: str
     o: str
     kind: str = "matrix_memory"
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """A selective state space per head behind a short convolution (the state-space-duality form, "Mamba-2"). With
+    inner = heads * head_dim, N = state_dim, G = groups, ``in_proj`` x is laid out [z: inner | x: inner | B: G N | C: G N |
+    dt: heads]. x, B and C together pass a causal convolution per channel (``conv`` [inner + 2 G N, taps], bias
+    ``conv_bias``, the last tap on the token itself) and silu. dt = softplus(dt + ``dt_bias``) without a clamp; per head
+    (head h reads group h // (heads // groups)), S_t = exp(-exp(``a_log``[h]) dt) S_(t-1) + dt B_t x_t^T (S: [N, head_dim]),
+    y_t = S_t^T C_t + ``skip``[h] x_t. y (heads side by side) is multiplied by silu(z), then divided in ``norm_groups``
+    equal parts by each part's root mean square (``norm_eps`` inside the root), times ``out_norm`` [inner], then ``o``.
+    The state and the convolution's last taps - 1 inputs are float32 and start at zero."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    state_dim: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    norm_eps: float
+    in_proj: str
+    conv: str
+    conv_bias: str
+    dt_bias: str
+    a_log: str
+    skip: str
+    out_norm: str
+    o: str
+    kind: str = "state_space"
+
+
+@dataclass(frozen=True)
+class GatedDeltaRuleSpec:
+    """A matrix state per head updated by the gated delta rule. q = ``q`` x and k = ``k`` x have ``num_qk_heads`` heads of
+    ``key_dim``, v = ``v`` x has ``num_heads`` heads of ``value_dim`` (head h reads query / key head h // (num_heads //
+    num_qk_heads)); each passes a short causal convolution per channel (``q_conv`` / ``k_conv`` / ``v_conv`` [channels,
+    taps], no bias) and silu. q and k become unit vectors per head, x / sqrt(sum(x^2) + 1e-6), q also times key_dim^-1/2.
+    Per head: strength = sigmoid(``strength`` x), decay = exp(-exp(``a_log``) softplus(``decay`` x + ``dt_bias``));
+    S <- decay S; u = strength (v - S^T k); S <- S + k u^T; o = S^T q. Each head's o is divided by its root mean square
+    over value_dim (``norm_eps``), times ``out_norm`` [value_dim] (shared by the heads), times silu(``gate`` x); then ``o``.
+    The state and the convolutions' last inputs are float32 and start at zero."""
+    hidden_size: int
+    num_heads: int
+    num_qk_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float
+    q: str
+    k: str
+    v: str
+    q_conv: str
+    k_conv: str
+    v_conv: str
+    strength: str
+    decay: str
+    a_log: str
+    dt_bias: str
+    gate: str
+    out_norm: str
+    o: str
+    kind: str = "gated_delta_rule"
+
+
+@dataclass(frozen=True)
+class MixerPairSpec:
+    """Two mixers side by side that read the same input: ``left_scale`` * left(x) + ``right_scale`` * right(x). Each
+    keeps its own cache or state."""
+    left: object
+    right: object
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    kind: str = "mixer_pair"
 
 
 @dataclass(frozen=True)
@@ -285,7 +380,13 @@ class ExpertRoutingSpec:
     may be chosen; the ``top`` largest scores among those win, and their weights are the scores divided by their sum.
 
     ``scoring="softmax_top"``: the ``top`` experts with the largest logits router x + ``router_bias`` are chosen, and
-    their weights are the softmax over the chosen logits alone (``groups`` and ``keep_groups`` stay 1)."""
+    their weights are the softmax over the chosen logits alone (``groups`` and ``keep_groups`` stay 1).
+
+    ``scoring="softmax_groups"``: scores softmax(router x) over all router outputs: the ``num_experts`` experts and
+    ``identity_experts`` further ones without tensors whose output is their input. The choice is made on score +
+    ``correction`` [all outputs]; a group's score is its largest choice score, the ``top`` largest choice scores inside
+    the ``keep_groups`` best groups win; the weights are the chosen scores (without the correction) times
+    ``weight_scale``, not renormalised."""
     num_experts: int
     top: int
     groups: int
@@ -293,6 +394,9 @@ class ExpertRoutingSpec:
     router: str
     scoring: str = "sigmoid_groups"
     router_bias: Optional[str] = None
+    correction: Optional[str] = None
+    weight_scale: float = 1.0
+    identity_experts: int = 0
 
 
 @dataclass(frozen=True)
@@ -393,12 +497,13 @@ class PostNormBlockSpec:
 class BlockSpec:
     """One layer: how its norms, mixer and feed-forward are arranged.
 
-    ``kind="prenorm"``: x += mixer(norm(x)); x += feed_forward(norm(x)).
+    ``kind="prenorm"``: x += mixer(norm(x)); x += feed_forward(norm(x)). ``ffn`` and ``ffn_norm`` may both be None (a
+    layer without a feed-forward).
     """
     mixer_norm: NormSpec
     mixer: object
-    ffn_norm: NormSpec
-    ffn: object
+    ffn_norm: Optional[NormSpec]
+    ffn: Optional[object]
     kind: str = "prenorm"
 
 
@@ -415,12 +520,13 @@ class EmbeddingSpec:
 @dataclass(frozen=True)
 class HeadSpec:
     """Final norm and projection to the vocabulary. ``weight`` may name the
-    embedding table (a tied head)."""
+    embedding table (a tied head). ``logit_scale`` multiplies the logits."""
     vocab_size: int
     hidden_size: int
     norm: NormSpec
     weight: str
     kind: str = "linear_head"
+    logit_scale: float = 1.0
 
 
 @dataclass(frozen=True)
