@@ -5,6 +5,7 @@
     python bench.py --design ramupel [--size s|m|l] [--layers N]      (the hybrid design beside Llama at equal size)
     python bench.py --design botuvik [--size s|m|l] [--layers N]      (the same for the Botuvik design, beside both)
     python bench.py --design zasitar [--size s|m|l] [--layers N]      (the Zasitar design beside Botuvik and Llama)
+    python bench.py --design dopuvik [--size s|m|l] [--layers N]      (the Dopuvik design beside Zasitar and Llama)
 
 One "step" is one decode step of the whole batch. The default run has the Llama-3.2-1B shape, a batch of 8
 sequences with 512-token prompts in a cache sized for a context of 4096. Every figure comes from the library's
@@ -28,6 +29,9 @@ the same width, depth, head count and feed-forward parameters, both with random 
 section of the model walk of each and what the mixers' core kernels reach of their rooflines.
 ``--design botuvik`` does the same for the Botuvik design (matrix-memory layers, capped attention with sinks, dense
 and routed feed-forwards) beside Ramupel, the closest existing design (a recurrence among attention layers), and Llama.
+``--design dopuvik`` does the same for the Dopuvik design (state-space layers, latent attention in a window, attention
+with kept first tokens beside a gated delta rule, experts chosen in groups with identity experts) beside Zasitar, the
+closest existing design (a recurrence among windowed attention layers, routed experts), and Llama.
 ``--design zasitar`` does the same for the Zasitar design (time-mixing layers, sliding-window attention with normed
 heads and keys shared between layers, results normed behind the sublayers) beside Botuvik, the closest existing design
 (a matrix recurrence among attention layers with sinks, dense and routed feed-forwards), and Llama.
@@ -219,6 +223,36 @@ def zasitar_config(size, layers):
     return {"architecture": "Zasitar", "vocab": 32000, "width": width, "norm": {"eps": 1e-5}, "layers": out}
 
 
+DOPUVIK_WINDOW, DOPUVIK_KEEP = 1024, 4
+
+
+def dopuvik_config(size, layers):
+    """Of every four layers the first is a state space (heads of 64 values over twice the width, states of 128, a
+    convolution of 4 taps), the second and fourth latent attention (the sizes of the Ramupel design's latent layers,
+    queries through a latent of 1.5 x the key / value rank, a window of DOPUVIK_WINDOW tokens, stretched rotation), the
+    third attention (grouped as in the Llama beside it, the same window plus DOPUVIK_KEEP kept first tokens) beside a
+    gated delta rule (as many heads of dim x dim as the Ramupel design's linear attention has, convolutions of 4 taps).
+    Every feed-forward is routed: 8 experts of a quarter of the dense width and 2 identities in 5 groups of which 3 are
+    kept, 2 chosen (the Zasitar beside it routes every second layer's and has a shared expert instead)."""
+    width, heads, (dn, dr, dv, rank), (gh, gk, _), ff = HYBRID_SIZES[size]
+    hd = width // heads
+    space = {"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": heads, "dim": dn, "rot_dim": dr, "vdim": dv, "kv_rank": rank, "q_rank": 3 * rank // 2,
+                        "scale": (dn + dr) ** -0.5, "mask": {"size": DOPUVIK_WINDOW},
+                        "rot": {"base": 10000.0, "dims": dr, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    pair = {"type": "parallel",
+            "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                               "mask": {"size": DOPUVIK_WINDOW, "keep_first": DOPUVIK_KEEP}, "rot": {"base": 10000.0, "dims": hd}},
+                      "right": {"heads": gh, "kv_heads": gh, "dim": gk, "vdim": gk, "conv": 4},
+                      "left_scale": 1.0, "right_scale": 1.0}}
+    routed = {"kind": "moe", "expert": {"ff": ff // 4},
+              "router": {"experts": 8, "identity": 2, "top": 2, "scale": 1.0, "groups": {"count": 5, "keep": 3}}}
+    order = (space, latent, pair, latent)
+    return {"architecture": "Dopuvik", "vocab": 32000, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "layers": [dict(order[i % 4], mlp=routed) for i in range(layers)]}
+
+
 def compare_designs(args, peaks) -> int:
     import torch
     from llmplayer_b200 import Engine
@@ -234,9 +268,9 @@ def compare_designs(args, peaks) -> int:
     gen = torch.Generator().manual_seed(5)
     clocks = ClockSampler()
     clocks.start()
-    botuvik, zasitar = args.design == "botuvik", args.design == "zasitar"
+    botuvik, zasitar, dopuvik = args.design == "botuvik", args.design == "zasitar", args.design == "dopuvik"
     title = {"botuvik": "Botuvik design beside Ramupel and ", "zasitar": "Zasitar design beside Botuvik and ",
-             "ramupel": "Ramupel design beside "}[args.design]
+             "ramupel": "Ramupel design beside ", "dopuvik": "Dopuvik design beside Zasitar and "}[args.design]
     out = {"metric": f"prefill and decode tok/s of the {title}Llama at equal size (bf16)", "impl": "ours",
            "layers": layers, "batch": batch, "prompt_len": prompt, "prefill_len": prefill_len, "peaks": peaks, "sizes": {}}
     try:
@@ -247,6 +281,8 @@ def compare_designs(args, peaks) -> int:
                 designs.insert(0, ("botuvik", botuvik_config(size, layers)))
             if zasitar:
                 designs = [("zasitar", zasitar_config(size, layers)), ("botuvik", botuvik_config(size, layers)), designs[1]]
+            if dopuvik:
+                designs = [("dopuvik", dopuvik_config(size, layers)), ("zasitar", zasitar_config(size, layers)), designs[1]]
             for name, raw in designs:
                 vocab = raw.get("vocab", raw.get("vocab_size"))
                 tmp = tempfile.mkdtemp(prefix="llmplayer_b200_bench_")
@@ -307,7 +343,9 @@ def compare_designs(args, peaks) -> int:
                 }
                 del engine, profiled
                 torch.cuda.empty_cache()
-            row["rooflines"] = {} if zasitar else hybrid_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len)
+            row["rooflines"] = {} if zasitar or dopuvik else hybrid_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len)
+            if dopuvik:
+                row["rooflines"].update(dopuvik_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len))
             if botuvik or zasitar:
                 row["rooflines"].update(botuvik_rooflines(size, layers, row, peaks, batch, prompt + 10, prefill_len))
             if zasitar:
@@ -422,6 +460,62 @@ def zasitar_rooflines(size, layers, row, peaks, batch, context, n):
     return out
 
 
+def dopuvik_rooflines(size, layers, row, peaks, batch, context, n):
+    """The Dopuvik kernels beside their Zasitar (and Llama) twins: prompt kernels against the bf16 tensor peak, decode
+    and elementwise kernels against the copy bandwidth. A windowed layer's work counts the keys inside the window (and
+    the kept first tokens) only."""
+    width, heads, (dn, dr, dv, rank), (gh, gk, _), ff = HYBRID_SIZES[size]
+    kinds = [i % 4 for i in range(layers)]
+    n_space, n_lat, n_pair = kinds.count(0), kinds.count(1) + kinds.count(3), kinds.count(2)
+    flops, gbs = peaks["bf16_tflops"] * 1e12, peaks["hbm_gbs"] * 1e9
+    d, z, l = row["dopuvik"], row.get("zasitar"), row.get("llama")
+    hd, G, W, K = width // heads, max(1, heads // 4), DOPUVIK_WINDOW, DOPUVIK_KEEP
+    sh, sp, sn = 2 * width // 64, 64, 128
+
+    def frac(work, ms, count, peak):
+        return None if not ms or not count else work / (ms / count / 1e3) / peak
+    seen = sum(min(i + 1, W) for i in range(n))                                   # (query, key) pairs inside the window
+    seen_kept = seen + sum(min(K, max(0, i + 1 - W)) for i in range(n))           # and the kept first tokens behind it
+    routed_rows = 8 * (ff // 4)
+    pre, dec = d["prefill_sections_ms"], d["decode_sections_ms"]
+    out = {
+        "prefill dopuvik latent attention, keys in the window (of tensor peak)": frac(
+            heads * seen * 2 * ((dn + dr) + dv), pre.get("attention.scores"), n_lat, flops),
+        "prefill dopuvik attention with kept tokens, keys seen (of tensor peak)": frac(
+            heads * seen_kept * 4 * hd, pre.get("left.attention.scores"), n_pair, flops),
+        "prefill dopuvik state-space recurrence (of tensor peak)": frac(6.0 * sh * sn * sp * n, pre.get("recurrence.scan"), n_space, flops),
+        "prefill dopuvik delta-rule recurrence (of tensor peak)": frac(8.0 * gh * gk * gk * n, pre.get("right.recurrence.scan"), n_pair, flops),
+        "prefill dopuvik routed gate/up product, all experts (of tensor peak)": frac(
+            2.0 * n * width * 2 * routed_rows, pre.get("ffn.gate_up"), layers, flops),
+        "prefill dopuvik short convolutions (of copy bandwidth)": frac(
+            n * (2 * width + 2 * sn) * 8, pre.get("recurrence.conv"), n_space, gbs),
+        "decode dopuvik latent attention (of copy bandwidth)": frac(
+            batch * min(context, W) * (rank + dr) * 2, dec.get("attention.scores"), n_lat, gbs),
+        "decode dopuvik attention with kept tokens (of copy bandwidth)": frac(
+            batch * min(context, W + K) * 2 * G * hd * 2, dec.get("left.attention.scores"), n_pair, gbs),
+        "decode dopuvik state-space recurrence (of copy bandwidth)": frac(batch * sh * sn * sp * 4 * 2, dec.get("recurrence.scan"), n_space, gbs),
+        "decode dopuvik delta-rule recurrence (of copy bandwidth)": frac(batch * gh * gk * gk * 4 * 2, dec.get("right.recurrence.scan"), n_pair, gbs),
+    }
+    if z is not None:
+        zh, zn = width // 64, 64
+        zpre, zdec = z["prefill_sections_ms"], z["decode_sections_ms"]
+        z_att = sum(1 for i in range(layers) if i % 4)
+        z_mix = layers - z_att
+        out["prefill zasitar attention, keys in the window (of tensor peak)"] = frac(heads * seen * 4 * hd, zpre.get("attention.scores"), z_att, flops)
+        out["prefill zasitar recurrence (of tensor peak)"] = frac(6.0 * zh * zn * zn * n, zpre.get("recurrence.scan"), z_mix, flops)
+        out["prefill zasitar routed gate/up product, all experts (of tensor peak)"] = frac(
+            2.0 * n * width * 2 * (8 * (ff // 4) + ff // 4), zpre.get("ffn.gate_up"), sum(1 for i in range(layers) if i % 2), flops)
+        out["decode zasitar attention (of copy bandwidth)"] = frac(
+            batch * min(context, ZASITAR_WINDOW) * 2 * G * hd * 2, zdec.get("attention.scores"), z_att, gbs)
+        out["decode zasitar recurrence (of copy bandwidth)"] = frac(batch * zh * zn * zn * 4 * 2, zdec.get("recurrence.scan"), z_mix, gbs)
+    if l is not None:
+        out["prefill llama attention (of tensor peak)"] = frac(
+            heads * n * (n + 1) * 2 * hd, l["prefill_sections_ms"].get("attention.scores"), layers, flops)
+        out["decode llama attention (of copy bandwidth)"] = frac(
+            batch * context * 2 * G * hd * 2, l["decode_sections_ms"].get("attention.scores"), layers, gbs)
+    return out
+
+
 def spread(values):
     return {"median": statistics.median(values), "min": min(values), "max": max(values), "repeats": len(values)}
 
@@ -442,8 +536,8 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true",
                     help="measure only the 2,048-token prefill (small runs for profiling)")
     ap.add_argument("--profile", action="store_true", help="add the device time per section of the model walk")
-    ap.add_argument("--design", default="llama", choices=("llama", "ramupel", "botuvik", "zasitar"),
-                    help="ramupel / botuvik / zasitar: that design beside the closest others at equal size (another workload; see "
+    ap.add_argument("--design", default="llama", choices=("llama", "ramupel", "botuvik", "zasitar", "dopuvik"),
+                    help="ramupel / botuvik / zasitar / dopuvik: that design beside the closest others at equal size (another workload; see "
                          "the module text)")
     ap.add_argument("--size", default=None, choices=sorted(HYBRID_SIZES), help="with --design ramupel / botuvik / zasitar: one size only")
     args = ap.parse_args()
@@ -456,7 +550,7 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU library")
         return 2
-    if args.design in ("ramupel", "botuvik", "zasitar"):
+    if args.design in ("ramupel", "botuvik", "zasitar", "dopuvik"):
         return compare_designs(args, load_peaks())
     args.warmup = max(3, args.warmup)
     repeats = max(1, args.repeats)

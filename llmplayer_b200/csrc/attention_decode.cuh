@@ -266,14 +266,20 @@ __device__ __forceinline__ void attention_decode_unit(
     // window) are cut into as many shares as leaves each at least min_share_pages, at most num_splits; the other
     // CTAs of the grid have nothing to do. A share and the merge of shares cost several dependent round trips
     // to memory, so a short sequence is better served by one CTA however wide its page table is.
-    int shares = num_splits, page_lo, page_hi;
+    // A window may keep the sequence's first `keep` tokens visible (fused.score.keep): the pages that hold them and lie
+    // before the window's pages are then visited first. A share's pages are counted in the order they are visited;
+    // the a-th visited page is page a of the table for a < kept_pages, else page first_win + (a - kept_pages).
+    const int keep_end = window > 0 ? min(max(fused.score.keep, 0), lo) : 0;      // keys [0, keep_end) are seen besides [lo, pos]
+    int shares = num_splits, page_lo, page_hi, kept_pages = 0, first_win = 0;
     if (min_share_pages > 0) {
         const int first = lo / PAGE, last = len > 0 ? pos / PAGE : first - 1;
-        const int total = last - first + 1;
+        kept_pages = min(first, (keep_end + PAGE - 1) / PAGE);
+        first_win = first;
+        const int total = kept_pages + last - first + 1;
         shares = max(1, min(num_splits, total / min_share_pages));
         const int per = (max(total, 1) + shares - 1) / shares;
-        page_lo = first + split * per;
-        page_hi = min(last, page_lo + per - 1);
+        page_lo = split * per;
+        page_hi = min(total - 1, page_lo + per - 1);
         if (split >= shares) {
             if (!FUSED) {                          // the separate merge kernel reads every share: leave an empty one
                 for (int r = tid; r < nrows; r += 32 * NW) {
@@ -288,6 +294,7 @@ __device__ __forceinline__ void attention_decode_unit(
         page_lo = max(lo / PAGE, split * pages_per_split);
         page_hi = len > 0 ? min(pos / PAGE, (split + 1) * pages_per_split - 1) : page_lo - 1;
     }
+    auto page_index = [&](int a) { return a < kept_pages ? a : first_win + (a - kept_pages); };
     const int* table = page_table + (size_t)b * pt_stride;
     const int stage_bytes = 2 * PAGE * hd * 2;
     const int npages = page_hi - page_lo + 1;      // may be <= 0: this share holds nothing of the sequence
@@ -297,11 +304,11 @@ __device__ __forceinline__ void attention_decode_unit(
     // The first warp keeps 32 entries of the page table in its lanes (entry p of the share in lane p % 32, loaded
     // 32 at a time), so that a request does not begin with a round trip to L2 for the page's number.
     int table_lane = 0, table_base = 0;
-    if (TMA && warp == 0 && lane < npages) table_lane = table[page_lo + lane];
+    if (TMA && warp == 0 && lane < npages) table_lane = table[page_index(page_lo + lane)];
     auto page_number = [&](int p) {                // called by the whole first warp
         if (p >= table_base + 32) {
             table_base = p & ~31;
-            table_lane = table_base + lane < npages ? table[page_lo + table_base + lane] : 0;
+            table_lane = table_base + lane < npages ? table[page_index(page_lo + table_base + lane)] : 0;
         }
         return __shfl_sync(0xffffffffu, table_lane, p & 31);
     };
@@ -334,7 +341,7 @@ __device__ __forceinline__ void attention_decode_unit(
 #pragma unroll
             for (int j = 0; j < PG; ++j) {
                 const int p = gi * PG + j;
-                if (p < npages) load_page(smem + p * stage_bytes, pages, table[page_lo + p], G, g, hd, tid, NT);
+                if (p < npages) load_page(smem + p * stage_bytes, pages, table[page_index(page_lo + p)], G, g, hd, tid, NT);
             }
             cp_async_commit();
         }
@@ -348,7 +355,8 @@ __device__ __forceinline__ void attention_decode_unit(
     __nv_bfloat16* new_v = new_k + hd;
     float* cs = reinterpret_cast<float*>(new_v + hd);
     float* sn = cs + 128;
-    const bool holds_new = FUSED && fused.pages_rw != nullptr && len > 0 && pos / PAGE >= page_lo && pos / PAGE <= page_hi;
+    const int new_page_at = kept_pages + pos / PAGE - first_win;      // where the new token's page comes among the visited ones
+    const bool holds_new = FUSED && fused.pages_rw != nullptr && len > 0 && new_page_at >= page_lo && new_page_at <= page_hi;
     if (FUSED) {
         const int half = fused.rd >> 1;
         for (int i = tid; i < half; i += NT) sincosf((float)pos * fused.inv_freq[i], &sn[i], &cs[i]);
@@ -449,7 +457,7 @@ __device__ __forceinline__ void attention_decode_unit(
     float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.f, l1 = 0.f;       // running maximum and sum of heads 2 t4 and 2 t4 + 1
 
     const int ngroups = (npages + PG - 1) / PG;
-    const int new_at = pos / PAGE - page_lo;         // which of the share's pages holds the new token
+    const int new_at = new_page_at - page_lo;        // which of the share's pages holds the new token
     const int cpr = hd >> 3;
     const int frag_row = (lane & 7) + ((lane >> 3) & 1) * 8, frag_chunk = lane >> 4;      // ldmatrix.x4 for a 16 x 16 row operand
     for (int gi = 0; gi < ngroups; ++gi) {
@@ -478,11 +486,11 @@ __device__ __forceinline__ void attention_decode_unit(
             if (!arrived && lane == 0) atomicExch(status, 6);
         }
         if (i < npages && arrived) {
-            const int key_base = (page_lo + i) * PAGE;
+            const int key_base = page_index(page_lo + i) * PAGE;
             const uint32_t k_tile = smem_u32(smem + (i % STAGES) * stage_bytes);
             const uint32_t v_tile = k_tile + PAGE * hd * 2;
             const int key0 = kw * 16;                    // this warp's 16 keys of its page
-            if (key_base + key0 <= pos && key_base + key0 + 15 >= lo) {
+            if (key_base + key0 <= pos && (key_base + key0 + 15 >= lo || key_base + key0 < keep_end)) {
                 // S^T: s[0], s[1] = key g8 with heads 2 t4, 2 t4 + 1; s[2], s[3] = key g8 + 8 with the same heads
                 float s[4] = {0.f, 0.f, 0.f, 0.f};
                 const int k_row = key0 + frag_row;
@@ -495,7 +503,7 @@ __device__ __forceinline__ void attention_decode_unit(
                     }
                 }
                 const int key_a = key_base + key0 + g8, key_b = key_a + 8;
-                const bool out_a = key_a > pos || key_a < lo, out_b = key_b > pos || key_b < lo;
+                const bool out_a = key_a > pos || (key_a < lo && key_a >= keep_end), out_b = key_b > pos || (key_b < lo && key_b >= keep_end);
                 s[0] = out_a ? NEG_BIG : shaped_score(s[0], scale_log2, fused.score);
                 s[1] = out_a ? NEG_BIG : shaped_score(s[1], scale_log2, fused.score);
                 s[2] = out_b ? NEG_BIG : shaped_score(s[2], scale_log2, fused.score);
@@ -551,7 +559,7 @@ __device__ __forceinline__ void attention_decode_unit(
             for (int j = 0; j < PG; ++j) {
                 const int nxt = (gi + GROUPS) * PG + j;
                 if (nxt < npages)
-                    load_page(smem + (nxt % STAGES) * stage_bytes, pages, table[page_lo + nxt], G, g, hd, tid, NT);
+                    load_page(smem + (nxt % STAGES) * stage_bytes, pages, table[page_index(page_lo + nxt)], G, g, hd, tid, NT);
             }
             cp_async_commit();
         }

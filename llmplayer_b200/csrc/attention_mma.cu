@@ -554,10 +554,11 @@ extern "C" long long lp_attention_decode_scratch(int B, int H, int hd, int num_s
 static int attention_decode_launch(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
                                    const int* kv_len, float* scratch, int B, int H, int G, int hd, int page_size,
                                    float scale, int window, int pages_per_split, int num_splits, int min_share_pages,
-                                   float softcap, const float* sinks, int split_weights, cudaStream_t stream) {
+                                   float softcap, const float* sinks, int split_weights, cudaStream_t stream, int keep = 0) {
     if (B <= 0) return 0;
+    if (keep > 0 && min_share_pages <= 0) LP_REFUSE("attention_decode: kept first tokens need shares fitted to the sequence (%d)", keep);
     FusedDecodeArgs plain_args{};
-    plain_args.score = make_extras(scale, softcap, sinks);
+    plain_args.score = make_extras(scale, softcap, sinks, window > 0 ? keep : 0);
     int rc = check_geometry("attention_decode", H, G, hd);
     if (rc) return rc;
     if (page_size != PAGE) LP_REFUSE("attention_decode: pages of %d positions (built for %d)", page_size, PAGE);
@@ -615,11 +616,12 @@ extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, 
 extern "C" int lp_attention_decode_fitted(const void* q, void* out, const void* pages, const int* page_table,
                                           int pt_stride, const int* kv_len, float* scratch, int B, int H, int G, int hd,
                                           int page_size, float scale, int window, int num_splits, int min_share_pages,
-                                          float softcap, const float* sinks, int split_weights, cudaStream_t stream) {
+                                          float softcap, const float* sinks, int split_weights, int keep,
+                                          cudaStream_t stream) {
     if (min_share_pages <= 0) LP_REFUSE("attention_decode_fitted: shares of at least %d pages", min_share_pages);
     return attention_decode_launch(q, out, pages, page_table, pt_stride, kv_len, scratch, B, H, G, hd, page_size, scale,
                                    window, pt_stride > 0 ? pt_stride : 1, num_splits, min_share_pages, softcap, sinks,
-                                   split_weights, stream);
+                                   split_weights, stream, keep);
 }
 
 // Decode attention that starts from the fused projection output: rotation of queries and of the new key,

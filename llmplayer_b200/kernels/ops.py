@@ -65,7 +65,7 @@ _SIGNATURES = {
     "attention_mma": {
         "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _F, _P, _I, _I, _P],
         "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
-        "lp_attention_decode_fitted": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _P],
+        "lp_attention_decode_fitted": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _I, _P],
         "lp_attention_decode_fused": [_P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
                                       _I, _I, _I, _P, _F, _I, ctypes.c_longlong, _P, _P],
     },
@@ -283,10 +283,32 @@ def set_profiler(profiler: Optional[StepProfiler]) -> None:
     _profiler = profiler
 
 
+_section_prefix = ""
+
+
+class section_prefix:
+    """``with ops.section_prefix("left."):`` around a part that runs inside another: the sections it opens are
+    reported under that prefix, so that two members of the same kind keep their times apart."""
+
+    def __init__(self, prefix: str):
+        self.prefix = prefix
+
+    def __enter__(self):
+        global _section_prefix
+        self.before = _section_prefix
+        _section_prefix = self.before + self.prefix
+        return self
+
+    def __exit__(self, *exc):
+        global _section_prefix
+        _section_prefix = self.before
+        return False
+
+
 def section(name: str):
     """``with ops.section("attention.qkv"):`` around the launches of one section of the model walk; costs
     nothing unless a profiler is set."""
-    return _NO_SECTION if _profiler is None else _profiler.section(name)
+    return _NO_SECTION if _profiler is None else _profiler.section(_section_prefix + name)
 
 
 _launches = 0
@@ -971,9 +993,10 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pa
                      kv_len: torch.Tensor, scratch, *, num_heads: int, num_kv_heads: int, head_dim: int,
                      scale: float, window: Optional[int], pages_per_split: int = 0, num_splits: int = 0,
                      softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
-                     exact_weights: bool = False) -> torch.Tensor:
+                     exact_weights: bool = False, keep_first: int = 0) -> torch.Tensor:
     """Tensor-core attention for a step of one token per sequence. ``scratch(name, shape, dtype)``
-    supplies the float32 buffer for the partial results of the shares."""
+    supplies the float32 buffer for the partial results of the shares. ``keep_first`` (with a window, shares fitted to
+    the sequences): the sequence's first ``keep_first`` tokens stay visible; their pages are visited first."""
     _check_attention(q, out, pages, page_table, num_heads, num_kv_heads, head_dim, "attention_decode")
     _want(kv_len, "attention_decode kv_len", torch.int32, 1)
     _check_sinks(sinks, num_heads, "attention_decode")
@@ -981,6 +1004,9 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pa
     if q.shape[0] != B or page_table.shape[0] != B:
         raise KernelError(f"attention_decode: {B} sequences, q {tuple(q.shape)}, table {tuple(page_table.shape)}")
     fitted = not pages_per_split or not num_splits
+    keep_first = int(keep_first) if window else 0
+    if keep_first and not fitted:
+        raise KernelError("attention_decode: kept first tokens need shares fitted to the sequences")
     if fitted:
         pages_per_split, num_splits = decode_split(B, num_kv_heads, num_heads, page_table.shape[1])
     buf = scratch("attention_partials", (B * num_heads * num_splits * (head_dim + 2),), torch.float32)
@@ -990,7 +1016,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pa
             q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1],
             kv_len.data_ptr(), buf.data_ptr(), B, num_heads, num_kv_heads, head_dim, pages.shape[3], float(scale),
             int(window) if window else 0, num_splits, MIN_SHARE_PAGES, float(softcap or 0.0), _ptr(sinks),
-            1 if exact_weights else 0, _stream()))
+            1 if exact_weights else 0, keep_first, _stream()))
         return out
     _check(lib, lib.lp_attention_decode(
         q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1], kv_len.data_ptr(),
@@ -1060,15 +1086,14 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page
               fast: bool, softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None,
               exact_weights: bool = False, keep_first: int = 0) -> torch.Tensor:
     """Attention of the step's tokens over the cache; picks the kernel for the step's shape. ``keep_first`` (with a
-    window): the first tokens of a sequence that stay visible beyond the window; one-token steps of such a layer run
-    on the plain kernel (a block per token and head walks the kept tokens and the window)."""
+    window): the first tokens of a sequence that stay visible beyond the window."""
     tensor_cores = (fast and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
                     and head_dim % 16 == 0 and head_dim <= 256)
     keep_first = int(keep_first) if window else 0
-    if tensor_cores and ctx.all_single and not keep_first:
+    if tensor_cores and ctx.all_single:
         return attention_decode(q, out, pages, page_table, ctx.kv_len, ctx.buffer, num_heads=num_heads,
                                 num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window,
-                                softcap=softcap, sinks=sinks, exact_weights=exact_weights)
+                                softcap=softcap, sinks=sinks, exact_weights=exact_weights, keep_first=keep_first)
     if tensor_cores and not ctx.all_single:
         return attention_prefill(q, out, pages, page_table, ctx.q_start, ctx.kv_len, ctx.max_new,
                                  num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale,

@@ -52,7 +52,7 @@ class MixerPair(Part):
         ask = getattr(self.left, "buffer_to_clear", None)
         return ask(ctx, tokens) if ask is not None else None
 
-    def _run(self, member, args, ctx, view, x, name: str):
+    def _run(self, member, args, ctx, view, x, name: str, prefix: str):
         """Run a member into a float32 buffer of its own; returns (buffer, the vector it left to the caller or None)."""
         y = ctx.buffer(name, (x.shape[0], self._width), torch.float32)
         kwargs = {}
@@ -63,7 +63,8 @@ class MixerPair(Part):
         later = "bias_later" in args and "overwrite" in args and getattr(member, "output_bias", None) is not None
         if later:
             kwargs["bias_later"] = True
-        member.forward(ctx, view, x, y, **kwargs)
+        with ops.section_prefix(prefix):
+            member.forward(ctx, view, x, y, **kwargs)
         return y, (member.output_bias if later else None)
 
     def forward(self, ctx, cache, x, residual: torch.Tensor, overwrite: bool = False) -> bool:
@@ -74,8 +75,8 @@ class MixerPair(Part):
         views = cache.members if cache is not None else (None, None)
         if overwrite:
             residual.zero_()
-        a, a_vec = self._run(self.left, self._args[0], ctx, views[0], x, "pair_left")
-        b, b_vec = self._run(self.right, self._args[1], ctx, views[1], x, "pair_right")
+        a, a_vec = self._run(self.left, self._args[0], ctx, views[0], x, "pair_left", "left.")
+        b, b_vec = self._run(self.right, self._args[1], ctx, views[1], x, "pair_right", "right.")
         with ops.section("mixer.sum"):
             ops.scaled_sum(residual, a, self.spec.left_scale, b, self.spec.right_scale, a_vector=a_vec, b_vector=b_vec)
         return False

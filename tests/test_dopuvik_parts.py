@@ -411,20 +411,24 @@ def run_kept(kind, qd, pages, table, length, new, window, keep, H, G, hd, scale)
     if kind == "plain":
         ops.attention_plain(qd, out, pages, table, i32([0] * new), i32(list(range(length - new, length))), num_heads=H,
                             num_kv_heads=G, head_dim=hd, scale=scale, window=window, keep_first=keep)
-    else:
+    elif kind == "prompt":
         ops.attention_prefill(qd, out, pages, table, i32([0, new]), i32([length]), new, num_heads=H, num_kv_heads=G,
                               head_dim=hd, scale=scale, window=window, exact_weights=True, keep_first=keep)
+    else:
+        ops.attention_decode(qd, out, pages, table, i32([length]), scratch, num_heads=H, num_kv_heads=G, head_dim=hd,
+                             scale=scale, window=window, exact_weights=True, keep_first=keep)
     return out
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,hd,length,new,window,keep", [(4, 2, 48, 200, 200, 9, 3), (8, 1, 64, 321, 321, 64, 70), (2, 2, 128, 400, 57, 128, 1),
                                                            (6, 2, 96, 700, 700, 33, 130), (5, 1, 16, 130, 130, 2, 5), (2, 1, 64, 400, 300, 40, 20),
-                                                           (3, 3, 16, 300, 1, 10, 64), (2, 2, 64, 260, 2, 65, 0), (2, 1, 64, 500, 500, 1, 1)])
+                                                           (3, 3, 16, 300, 1, 10, 64), (2, 2, 64, 260, 2, 65, 0), (2, 1, 64, 500, 500, 1, 1),
+                                                           (8, 1, 64, 900, 1, 64, 70), (6, 2, 128, 1000, 1, 200, 130), (4, 4, 32, 1000, 1, 40, 0)])
 def test_attention_with_kept_first_tokens(dtype, H, G, hd, length, new, window, keep):
     """The last ``new`` tokens of a sequence of ``length`` see their window AND the sequence's first ``keep`` tokens
     (pages in a scrambled order; the pages between the kept ones and the window are not in the table at all): the
-    plain kernel in float32 and bfloat16, the tensor-core prompt kernel in bfloat16. One kept token more or fewer differs."""
+    plain kernel in float32 and bfloat16, the tensor-core prompt and decode kernels in bfloat16. One kept token more or fewer differs."""
     torch.manual_seed(length + hd + keep)
     scale = 0.3
     q = torch.randn(new, H, hd).to(dtype)
@@ -437,7 +441,7 @@ def test_attention_with_kept_first_tokens(dtype, H, G, hd, length, new, window, 
     table = i32([listed + [0] * (16 - len(listed))])
     ref = plain_kept_attention(q.double(), k.double(), v.double(), scale, window, keep, length - new)
     qd = q.reshape(new, H * hd).cuda()
-    kinds = [("plain", 3e-6)] if dtype == torch.float32 else [("plain", 6e-3)] + ([("prompt", 6e-3)] if new > 1 else [])
+    kinds = [("plain", 3e-6)] if dtype == torch.float32 else [("plain", 6e-3), ("prompt", 6e-3) if new > 1 else ("decode", 6e-3)]
     for kind, lim in kinds:
         out = run_kept(kind, qd, pages, table, length, new, window, keep, H, G, hd, scale)
         check_error(f"attention with kept first tokens, {kind} kernel, {dtype}", f"{H}/{G} x {hd}, {new} of {length}, window {window}, "
@@ -476,7 +480,7 @@ def test_a_key_at_the_edges_of_window_and_kept_tokens(dtype, step, length, windo
         pages = fill_pages(k, v, rows, 16, dtype)
         table = i32([rows + [0] * (16 - len(rows))])
         qd = q.reshape(new, H * hd).cuda()
-        kind = "plain" if dtype == torch.float32 or step == "decode" else "prompt"
+        kind = "plain" if dtype == torch.float32 else step
         out = run_kept(kind, qd, pages, table, length, new, window, keep, H, G, hd, scale).view(new, H, hd)
         ref = plain_kept_attention(q.double(), k.double(), v.double(), scale, window, keep, length - new)
         check_error(f"kept first tokens, a key that stands out, {step}, {dtype}", f"length {length}, window {window}, keep {keep}, key at {at}",
