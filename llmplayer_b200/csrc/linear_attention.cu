@@ -78,7 +78,7 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
                 float* __restrict__ out, int H, int dk, int dv, float q_scale, int mode, int chunks, int chunk,
                 float* __restrict__ chunk_state, float* __restrict__ chunk_decay, int decay_per_head,
                 const float* __restrict__ key_gain, int ones, const float* __restrict__ bonus, int qk_group,
-                const float* __restrict__ beta) {
+                const float* __restrict__ beta, int state_cols) {
     extern __shared__ float sm[];
     float* qs = sm;                         // [TB][dk]
     float* ks = qs + TB * dk;
@@ -97,8 +97,13 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
         t1 = min(t1, t0 + chunk);
         if (t0 >= t1) return;                             // this sequence has fewer chunks
     }
+    // The delta rule in chunks side by side: a chunk's effect on the state that enters it is S -> P S + L with P a
+    // [dk, dk] matrix (the product of the tokens' a (I - b k k^T)). Pass LOCAL therefore carries dk more columns per
+    // head: they start as the identity, are fed the value 0, and end as P (column m of P in column dv + m);
+    // `state_cols` = dv + dk is then how many columns a head has in `chunk_state` (else dv).
+    const int cols = (beta && mode == SCAN_LOCAL) ? dv + dk : dv;
     float* S = mode == SCAN_WHOLE ? state + ((long long)slots[b] * H + h) * dv * dk
-                                  : chunk_state + ((long long)blockIdx.z * H + h) * dv * dk;
+                                  : chunk_state + ((long long)blockIdx.z * H + h) * state_cols * dk;
     float s[KPT][JT], prod[KPT], ub[KPT];
 #pragma unroll
     for (int i = 0; i < KPT; ++i) {
@@ -106,7 +111,8 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
         ub[i] = (bonus && c < dk) ? bonus[(long long)h * dk + c] : 0.f;
 #pragma unroll
         for (int jj = 0; jj < JT; ++jj)
-            s[i][jj] = (mode != SCAN_LOCAL && j0 + jj < dv && c < dk) ? S[(long long)(j0 + jj) * dk + c] : 0.f;
+            s[i][jj] = (mode != SCAN_LOCAL && j0 + jj < dv && c < dk) ? S[(long long)(j0 + jj) * dk + c]
+                       : ((beta && mode == SCAN_LOCAL && j0 + jj >= dv && c == j0 + jj - dv) ? 1.f : 0.f);
         prod[i] = 1.f;
     }
     for (int tb = t0; tb < t1; tb += TB) {
@@ -182,9 +188,11 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
                         for (int jj = 0; jj < JT; ++jj) s[u][jj] = fmaf(a, s[u][jj], k * w[jj]);
                     }
                 }
+                if (mode != SCAN_LOCAL) {
 #pragma unroll
-                for (int jj = 0; jj < JT; ++jj)
-                    if (part == jj % KP && j0 + jj < dv) out[((long long)(tb + i) * H + h) * dv + j0 + jj] = acc[jj];
+                    for (int jj = 0; jj < JT; ++jj)
+                        if (part == jj % KP && j0 + jj < dv) out[((long long)(tb + i) * H + h) * dv + j0 + jj] = acc[jj];
+                }
                 continue;
             }
 #pragma unroll
@@ -227,8 +235,8 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
         const int c = part + KP * i;
 #pragma unroll
         for (int jj = 0; jj < JT; ++jj)
-            if (j0 + jj < dv && c < dk) S[(long long)(j0 + jj) * dk + c] = s[i][jj];
-        if (mode == SCAN_LOCAL && blockIdx.x == 0 && jg == 0 && c < dk)
+            if (j0 + jj < cols && c < dk) S[(long long)(j0 + jj) * dk + c] = s[i][jj];
+        if (mode == SCAN_LOCAL && !beta && blockIdx.x == 0 && jg == 0 && c < dk)
             chunk_decay[((long long)blockIdx.z * H + h) * dk + c] = prod[i];
     }
 }
@@ -257,6 +265,37 @@ gla_combine_kernel(float* __restrict__ state, const int* __restrict__ slots, con
         s = fmaf(chunk_decay[(((long long)b * chunks + p) * H + h) * dk + c], s, local);
     }
     *row = s;
+}
+
+// The delta rule's chunks in order: start_(p+1) = P_p start_p + L_p, column by column. One block per (value column,
+// head, sequence) with a thread per key channel; the column of the current start state lies in shared memory. Each
+// chunk's start state is put where its L was (columns 0 .. dv - 1 of the chunk's block), the last into the state row.
+__global__ void __launch_bounds__(512)
+delta_combine_kernel(float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ q_start,
+                     float* __restrict__ chunk_state, int H, int dk, int dv, int chunks, int chunk) {
+    __shared__ float col[512];
+    lp_grid_release();
+    lp_grid_wait();
+    const int j = blockIdx.x, h = blockIdx.y, b = blockIdx.z, c = threadIdx.x;
+    const int n = q_start[b + 1] - q_start[b];
+    const int used = (n + chunk - 1) / chunk;
+    const long long per = (long long)(dv + dk) * dk;
+    float* row = state + (((long long)slots[b] * H + h) * dv + j) * dk;
+    float mine = c < dk ? row[c] : 0.f;
+    for (int p = 0; p < used; ++p) {
+        if (c < dk) col[c] = mine;
+        __syncthreads();
+        float* blockp = chunk_state + (((long long)b * chunks + p) * H + h) * per;
+        if (c < dk) {
+            float acc = blockp[(long long)j * dk + c];                    // L_p[c][j]
+            const float* P = blockp + (long long)dv * dk + c;             // P_p[c][m] lies at column dv + m, channel c
+            for (int m = 0; m < dk; ++m) acc = fmaf(P[(long long)m * dk], col[m], acc);
+            blockp[(long long)j * dk + c] = mine;                         // the chunk's start state
+            mine = acc;
+        }
+        __syncthreads();
+    }
+    if (c < dk) row[c] = mine;
 }
 
 // ---------------------------------------------------------------- exponential gates with a running maximum
@@ -611,11 +650,11 @@ extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
     if (qk_heads <= 0) qk_heads = H;
     if (H % qk_heads) LP_REFUSE("gla_scan: %d heads over %d query / key heads", H, qk_heads);
     const int qk_group = H / qk_heads;
-    if (beta && (chunks > 1 || !decay_per_head || bonus || ones))
-        LP_REFUSE("gla_scan: the delta rule runs in one pass with one decay per head (chunks %d)", chunks);
+    const int state_cols = (beta && chunks > 1) ? dv + dk : dv;      // columns of a head in `chunk_state`
+    if (beta && (!decay_per_head || bonus || ones)) LP_REFUSE("gla_scan: the delta rule takes one decay per head and no bonus");
     ones = ones ? 1 : 0;
     if (dv - ones <= 0) LP_REFUSE("gla_scan: %d value columns, %d of them constant", dv, ones);
-    if (chunks > 1 && (chunk <= 0 || !chunk_state || !chunk_decay)) LP_REFUSE("gla_scan: %d chunks without their buffers", chunks);
+    if (chunks > 1 && (chunk <= 0 || !chunk_state || (!chunk_decay && !beta))) LP_REFUSE("gla_scan: %d chunks without their buffers", chunks);
     if ((long long)B * chunks > 65535) LP_REFUSE("gla_scan: %d sequences in %d chunks exceed the grid", B, chunks);
     if (H <= 0 || H > 65535 || B > 65535 || dk <= 0 || dv <= 0) LP_REFUSE("gla_scan: %d sequences, %d heads of %d x %d", B, H, dk, dv);
     if (dk > 512) LP_REFUSE("gla_scan: %d key channels per head (supported: up to 512)", dk);
@@ -632,17 +671,22 @@ extern "C" int lp_gla_scan(const float* proj, int ld, int q_off, int k_off, int 
         if (chunks == 1) {                                                                                            \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_WHOLE, 1, 0, (float*)nullptr,       \
-                      (float*)nullptr, decay_per_head, key_gain, ones, bonus, qk_group, beta);                                                                               \
+                      (float*)nullptr, decay_per_head, key_gain, ones, bonus, qk_group, beta, state_cols);                                                                               \
         } else {                                                                                                      \
-            lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
+            dim3 grid_local((state_cols + VT_ - 1) / VT_, H, B * chunks);                                             \
+            lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid_local, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_LOCAL, chunks, chunk, chunk_state,  \
-                      chunk_decay, decay_per_head, key_gain, ones, bonus, qk_group, beta);                                                                                   \
+                      chunk_decay, decay_per_head, key_gain, ones, bonus, qk_group, beta, state_cols);                                                                                   \
             const long long per = (long long)H * dv * dk;                                                             \
-            lp_launch(gla_combine_kernel, dim3((unsigned)((per + 255) / 256), B), 256, 0, stream, state, slots,       \
-                      q_start, chunk_state, (const float*)chunk_decay, H, dk, dv, chunks, chunk);                     \
+            if (beta)                                                                                                 \
+                lp_launch(delta_combine_kernel, dim3(dv, H, B), (dk + 31) / 32 * 32, 0, stream, state, slots, q_start, \
+                          chunk_state, H, dk, dv, chunks, chunk);                                                     \
+            else                                                                                                      \
+                lp_launch(gla_combine_kernel, dim3((unsigned)((per + 255) / 256), B), 256, 0, stream, state, slots,   \
+                          q_start, chunk_state, (const float*)chunk_decay, H, dk, dv, chunks, chunk);                 \
             lp_launch(gla_scan_kernel<KP_, VT_, N, JT_>, grid, VT_ / JT_ * KP_, smem, stream, proj, ld, q_off, k_off, v_off,     \
                       decay, state, slots, q_start, out, H, dk, dv, q_scale, SCAN_OUTPUT, chunks, chunk, chunk_state, \
-                      chunk_decay, decay_per_head, key_gain, ones, bonus, qk_group, beta);                                                                                   \
+                      chunk_decay, decay_per_head, key_gain, ones, bonus, qk_group, beta, state_cols);                                                                                   \
         }                                                                                                             \
     } while (0)
     // few key channels: 4 threads per column, 64 columns per CTA; from 32 channels on: 16 threads per column, 16 columns

@@ -1355,8 +1355,9 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
     token itself, out_t = (S + diag(bonus) k_t v_t^T)^T q_t, and the state is updated afterwards.
     ``qk_heads``: the projection holds that many query / key heads (a divisor of ``num_heads``); head h reads query / key
     head h // (num_heads // qk_heads). ``delta_strength``: float32 [T, H]; the recurrence is then the gated delta rule
-    (one decay a per head): S <- a S; u = strength * (v - S^T k); S <- S + k u^T; out = S^T q, in one pass over the
-    tokens (no chunks side by side)."""
+    (one decay a per head): S <- a S; u = strength * (v - S^T k); S <- S + k u^T; out = S^T q; long prompts run in
+    chunks side by side here too (a chunk's effect on the state that enters it is S -> P S + L with a [dk, dk] matrix P,
+    which the first pass forms beside L)."""
     _want(proj, "gla_scan proj", torch.float32, 2)
     _want(decay, "gla_scan decay", torch.float32, 2)
     _want(state, "gla_scan state", torch.float32, 4)
@@ -1383,18 +1384,20 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
         if delta_strength.shape != (T, H) or not decay_per_head:
             raise KernelError(f"gla_scan: write strengths {tuple(delta_strength.shape)} for {T} tokens and {H} heads "
                               f"(the delta rule takes one decay per head)")
-        scratch = None
     if qk_heads is not None and (qk_heads <= 0 or H % qk_heads):
         raise KernelError(f"gla_scan: {H} heads over {qk_heads} query / key heads")
     chunks, chunk_state, chunk_decay = 1, None, None
-    if scratch is not None and max_new >= GLA_CHUNKED_FROM and B * -(-max_new // GLA_CHUNK) <= 65535:
-        chunks = -(-max_new // GLA_CHUNK)
-        chunk_state = scratch("gla_chunk_states", (B, chunks, H, dv, dk), torch.float32)
-        chunk_decay = scratch("gla_chunk_decays", (B, chunks, H, dk), torch.float32)
+    # the delta rule's passes are bound by their chain of tokens, not by arithmetic: shorter chunks, more of them
+    chunk = GLA_CHUNK // 2 if delta_strength is not None else GLA_CHUNK
+    if scratch is not None and max_new >= GLA_CHUNKED_FROM and B * -(-max_new // chunk) <= 65535:
+        chunks = -(-max_new // chunk)
+        # the delta rule's chunks also carry their [dk, dk] transition, as dk more columns per head
+        chunk_state = scratch("gla_chunk_states", (B, chunks, H, dv + (dk if delta_strength is not None else 0), dk), torch.float32)
+        chunk_decay = scratch("gla_chunk_decays", (B, chunks, H, dk), torch.float32) if delta_strength is None else None
     lib = library("linear_attention")
     _check(lib, lib.lp_gla_scan(proj.data_ptr(), proj.shape[1], int(q_off), int(k_off), int(v_off), decay.data_ptr(),
                                 state.data_ptr(), slots.data_ptr(), q_start.data_ptr(), out.data_ptr(), B, H, dk, dv,
-                                float(q_scale), chunks, GLA_CHUNK, _ptr(chunk_state), _ptr(chunk_decay),
+                                float(q_scale), chunks, chunk, _ptr(chunk_state), _ptr(chunk_decay),
                                 1 if decay_per_head else 0, _ptr(key_gain), 1 if ones_column else 0, _ptr(bonus),
                                 int(qk_heads or H), _ptr(delta_strength), _stream()))
     if chunks > 1:

@@ -11,7 +11,9 @@ so the read-out sees the token's own write. Each head's o_t is divided by its ro
 shared by the heads and by silu(W_g x_t), and projected. State, decays, strengths, unit norms and every sum are float32.
 The recurrence is one more form of the framework's linear-attention scan (csrc/linear_attention.cu): a value column's
 state entries live in the registers of a few threads, and the two read-outs S^T k and S^T q of a token are taken from
-the state before it in one round of shuffles. What a sequence carries from step to step is S and the convolutions'
+the state before it in one round of shuffles; prompts of 256 tokens or more run in chunks of 128 side by side (a
+chunk's effect on the state that enters it is S -> P S + L; the first pass forms P, a [key_dim, key_dim] matrix, beside
+L, the chunks' start states follow in order, the second pass writes the outputs). What a sequence carries from step to step is S and the convolutions'
 last taps - 1 inputs. All kernels read the step from device tensors.
 """
 from __future__ import annotations
@@ -112,8 +114,8 @@ class GatedDeltaRule(Part):
         raw = ctx.buffer("recurrence_raw", (T, self.values), torch.float32)
         with ops.section("recurrence.scan"):
             ops.gla_scan(mixed, 0, self.qk, 2 * self.qk, gates[0], state, ctx.slots, ctx.q_start, raw, num_heads=H,
-                         key_dim=dk, value_dim=dv, q_scale=1.0, max_new=ctx.max_new, decay_per_head=True, qk_heads=G,
-                         delta_strength=gates[1])
+                         key_dim=dk, value_dim=dv, q_scale=1.0, max_new=ctx.max_new, scratch=ctx.buffer, decay_per_head=True,
+                         qk_heads=G, delta_strength=gates[1])
         o = ctx.buffer("attn_out", (T, self.values), rt.act_dtype)
         with ops.section("recurrence.norm"):
             clear = residual if overwrite and residual.dtype == torch.float32 and self.out.needs_zero(T) else None

@@ -239,9 +239,11 @@ def plain_delta_rule(q, k, v, beta, g, S):
 
 @pytest.mark.parametrize("H,G,dk,dv", [(4, 2, 20, 12), (2, 1, 16, 24), (2, 2, 128, 128), (4, 2, 64, 32), (1, 1, 6, 10), (3, 3, 256, 40)])
 def test_delta_rule_over_steps_and_slots(H, G, dk, dv):
+    """Steps of 1, 2, 30, 117 and 300 tokens (the last in chunks side by side, each chunk with its transition matrix)
+    for two sequences in slots 2 and 3; slots 0 and 1 stay as they were."""
     from llmplayer_b200.kernels import ops
     torch.manual_seed(dk + dv)
-    lengths = [120, 33]
+    lengths = [420, 333]             # the last step is long enough for chunks side by side, from a state that is not zero
     state = torch.zeros(4, H, dv, dk, device="cuda")
     state[0] = -4.0
     data = []
@@ -253,7 +255,7 @@ def test_delta_rule_over_steps_and_slots(H, G, dk, dv):
         ref = plain_delta_rule(q.double(), k.double(), v.double(), beta.double(), g.double(), S)
         data.append((q, k, v, beta, g, ref, S))
     done, got = [0, 0], [[], []]
-    for step in ([1, 1], [2, 30], [117, 2]):
+    for step in ([1, 1], [2, 30], [117, 2], [300, 300]):
         cat = lambda j: torch.cat([d[j][done[i]:done[i] + step[i]].reshape(step[i], -1) for i, d in enumerate(data)])
         mixed = torch.cat([cat(0), cat(1), cat(2)], dim=1).cuda()
         out = torch.empty(sum(step), H * dv, device="cuda")
