@@ -93,9 +93,9 @@ class LatentAttention(Part):
         """The matrices that multiply the mixer's input, in the order ``forward_projected`` expects their sums."""
         return list(self._inputs)
 
-    def forward_projected(self, ctx, cache, proj: torch.Tensor, offset: int, out: torch.Tensor) -> torch.Tensor:
+    def forward_projected(self, ctx, cache, proj: torch.Tensor, offset: int, out: torch.Tensor, add: bool = False) -> torch.Tensor:
         """``proj``: float32 [T, F] holding, from column ``offset``, the sums of :meth:`input_projections`;
-        writes the mixer's result (before any residual gate) to ``out`` float32 [T, hidden]."""
+        writes the mixer's result (before any residual gate) to ``out`` float32 [T, hidden] (``add``: adds it there)."""
         s, rt = self.spec, self.runtime
         if cache is None:
             raise ConfigError("latent attention needs its cache of latent rows")
@@ -118,7 +118,7 @@ class LatentAttention(Part):
                 self.q_up.store(q_latent, q_from, ctx)
         q = ctx.buffer("latent_q", (T, H, dn + dr), torch.float32)
         if self._forms_heads(ctx, cache):
-            return self._forward_heads(ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out, q_from)
+            return self._forward_heads(ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out, q_from, add)
         with ops.section("attention.position"):
             ops.latent_prepare(proj, q_off, kv_off, self.latent_gain, s.norm_eps, rotation, ctx.positions, ctx.seq_ids,
                                table, q, cache.pages, num_heads=H, nope_dim=dn, rope_dim=dr, kv_rank=rank, q_from=q_from)
@@ -134,7 +134,7 @@ class LatentAttention(Part):
                               kv_rank=rank, scale=s.scale, window=s.window)
         o = ctx.buffer("attn_out", (T, H * dv), rt.act_dtype)
         gate = proj[:, gate_off:gate_off + H] if s.out_gate is not None else None
-        clear = self._out_to_clear(ctx, T, out)
+        clear = None if add else self._out_to_clear(ctx, T, out)
         with ops.section("attention.values"):
             if shares > 2 and T > ops.LATENT_ROWS_FORM_TOKENS:
                 # many shares in a long step: one CTA per row merges them, so that the value map's CTAs (a tile of
@@ -145,7 +145,10 @@ class LatentAttention(Part):
         if clear is not None:
             ctx.note_cleared()
         with ops.section("attention.out"):
-            self.out.store(o, out, ctx)
+            if add:
+                self.out.accumulate(o, out, ctx)
+            else:
+                self.out.store(o, out, ctx)
         return out
 
     def _out_to_clear(self, ctx, tokens: int, out: torch.Tensor):
@@ -173,7 +176,7 @@ class LatentAttention(Part):
         need = self.spec.nope_dim + self.spec.rope_dim
         return next((size for size in (64, 128, 192, 256) if need <= size), None)
 
-    def _forward_heads(self, ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out, q_from=None):
+    def _forward_heads(self, ctx, cache, proj, q_off, kv_off, gate_off, rotation, table, q, out, q_from=None, add=False):
         s = self.spec
         T = proj.shape[0]
         H, dn, dr, dv, rank = s.num_heads, s.nope_dim, s.rope_dim, s.value_dim, s.kv_rank
@@ -210,13 +213,16 @@ class LatentAttention(Part):
                                   exact_weights=s.exact_weights)
         o = ctx.buffer("attn_out", (T, H * dv), torch.bfloat16)
         gate = proj[:, gate_off:gate_off + H] if s.out_gate is not None else None
-        clear = self._out_to_clear(ctx, T, out)
+        clear = None if add else self._out_to_clear(ctx, T, out)
         with ops.section("attention.values"):
             ops.latent_gate_heads(heads, gate, o, num_heads=H, head_dim=hd, value_dim=dv, clear=clear)
         if clear is not None:
             ctx.note_cleared()
         with ops.section("attention.out"):
-            self.out.store(o, out, ctx)
+            if add:
+                self.out.accumulate(o, out, ctx)
+            else:
+                self.out.store(o, out, ctx)
         return out
 
     def buffer_to_clear(self, ctx, tokens: int):
@@ -233,9 +239,7 @@ class LatentAttention(Part):
         proj = ctx.buffer("mixer_proj", (x.shape[0], self._own.out_features), torch.float32)
         with ops.section("attention.qkv"):
             self._own.store(x, proj, ctx)
-        out = ctx.buffer("mixer_out", tuple(residual.shape), torch.float32)
-        self.forward_projected(ctx, cache, proj, 0, out)
-        ops.gated_sum(residual, out)
+        self.forward_projected(ctx, cache, proj, 0, residual, add=True)      # the output product adds into the stream itself
         return False
 
 
