@@ -180,7 +180,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 // approximation (relative error 2^-22, far below bfloat16's), and the tiles with the most keys
 // (the last ones of a prompt) are started first.
 template <int HD, int ROWS, bool SPLIT = false>
-__global__ void __launch_bounds__(ROWS * 2, SPLIT ? 3 : 1)
+__global__ void __launch_bounds__(ROWS * 2, (SPLIT && HD <= 128) ? 3 : 1)
 attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                                const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table,
                                int pt_stride, const int* __restrict__ q_start, const int* __restrict__ kv_len, int H,
@@ -525,6 +525,7 @@ extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages,
     } while (0)
         if (hd == 64) LP_PREFILL_EXACT_SPLIT(64, 64);
         else if (hd == 128) LP_PREFILL_EXACT_SPLIT(128, 64);
+        else if (hd == 192) LP_PREFILL_EXACT_SPLIT(192, 64);      // heads of 128 + 64 (latent attention in its head form)
         else if (hd <= 64) LP_PREFILL_SPLIT(64); else if (hd <= 96) LP_PREFILL_SPLIT(96); else if (hd <= 128) LP_PREFILL_SPLIT(128);
         else if (hd <= 192) LP_PREFILL_SPLIT(192); else LP_PREFILL_SPLIT(256);
 #undef LP_PREFILL_EXACT_SPLIT

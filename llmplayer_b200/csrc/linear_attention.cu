@@ -289,7 +289,15 @@ delta_combine_kernel(float* __restrict__ state, const int* __restrict__ slots, c
         if (c < dk) {
             float acc = blockp[(long long)j * dk + c];                    // L_p[c][j]
             const float* P = blockp + (long long)dv * dk + c;             // P_p[c][m] lies at column dv + m, channel c
-            for (int m = 0; m < dk; ++m) acc = fmaf(P[(long long)m * dk], col[m], acc);
+            int m = 0;
+            for (; m + 8 <= dk; m += 8) {                                 // eight loads in flight: a block has few warps
+                float pv[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) pv[u] = __ldcg(P + (long long)(m + u) * dk);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc = fmaf(pv[u], col[m + u], acc);
+            }
+            for (; m < dk; ++m) acc = fmaf(__ldcg(P + (long long)m * dk), col[m], acc);
             blockp[(long long)j * dk + c] = mine;                         // the chunk's start state
             mine = acc;
         }
