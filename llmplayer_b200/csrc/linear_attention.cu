@@ -144,7 +144,7 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
             const float* ai = as + i * dk;
             if (beta) {
                 // the delta rule (one decay a per head): S <- a S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
-                // Both read-outs are taken from the state before the token, S^T k and S^T q, in one round of
+                // Both read-outs are taken from the state before the token, S^T k and S^T q, in one pass of
                 // shuffles: the decayed S^T k is a (S^T k), and o = a (S^T q) + u (k . q).
                 float r1[JT], r2[JT], kq = 0.f;
 #pragma unroll

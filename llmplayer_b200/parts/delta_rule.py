@@ -11,7 +11,7 @@ so the read-out sees the token's own write. Each head's o_t is divided by its ro
 shared by the heads and by silu(W_g x_t), and projected. State, decays, strengths, unit norms and every sum are float32.
 The recurrence is one more form of the framework's linear-attention scan (csrc/linear_attention.cu): a value column's
 state entries live in the registers of a few threads, and the two read-outs S^T k and S^T q of a token are taken from
-the state before it in one round of shuffles; prompts of 256 tokens or more run in chunks of 128 side by side (a
+the state before it in one pass of shuffles; prompts of 256 tokens or more run in chunks of 128 side by side (a
 chunk's effect on the state that enters it is S -> P S + L; the first pass forms P, a [key_dim, key_dim] matrix, beside
 L, the chunks' start states follow in order, the second pass writes the outputs). What a sequence carries from step to step is S and the convolutions'
 last taps - 1 inputs. All kernels read the step from device tensors.
