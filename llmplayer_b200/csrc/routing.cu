@@ -71,13 +71,35 @@ route_kernel(const float* __restrict__ z, int ldz, float* __restrict__ weights, 
 }
 
 // hidden[t, c] *= weights[t, c / ff] for c < E * ff (in place; the columns beyond belong to experts every token uses)
+// Experts that are the identity ride along in the same launch: x[t, :] += h[t, :] * sum of the token's weights for them
+// (columns first .. first + count - 1 of the weights). x: float32 [T, d], the stream the experts' outputs are added to
+// by the product that follows; h: the feed-forward's input [T, d].
+struct IdentityShare {
+    float* x;
+    const void* h;
+    int h_bf16, first, count, d;
+};
+__device__ __forceinline__ void add_identity_share(const IdentityShare& id, const float* __restrict__ weights, int ldw, long long t,
+                                                   int begin, int stride) {
+    float w = 0.f;
+    for (int e = 0; e < id.count; ++e) w += weights[t * ldw + id.first + e];
+    if (w == 0.f) return;
+    for (int i = begin; i < id.d; i += stride) {
+        const float hv = id.h_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(id.h)[t * id.d + i])
+                                   : reinterpret_cast<const float*>(id.h)[t * id.d + i];
+        id.x[t * id.d + i] = fmaf(hv, w, id.x[t * id.d + i]);
+    }
+}
+
 template <typename TH>
 __global__ void __launch_bounds__(256)
 expert_scale_kernel(TH* __restrict__ hidden, int ldh, const float* __restrict__ weights, int ldw, int T, int E, int ff,
-                    float* __restrict__ zero, long long zero_count) {
+                    float* __restrict__ zero, long long zero_count, IdentityShare id) {
     lp_grid_release();
     lp_grid_wait();
     clear_on_the_side(zero, zero_count);
+    if (id.x)                                    // a block per token at a time
+        for (long long t = blockIdx.x; t < T; t += gridDim.x) add_identity_share(id, weights, ldw, t, threadIdx.x, blockDim.x);
     const long long cols = (long long)E * ff;
     const long long n = (long long)T * cols;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -91,11 +113,12 @@ expert_scale_kernel(TH* __restrict__ hidden, int ldh, const float* __restrict__ 
 // The same, eight bfloat16 columns of one expert per thread (expert sizes and rows of a multiple of eight values).
 __global__ void __launch_bounds__(256)
 expert_scale_vec8_kernel(__nv_bfloat16* __restrict__ hidden, int ldh, const float* __restrict__ weights, int ldw, int E, int ff,
-                         float* __restrict__ zero, long long zero_count) {
+                         float* __restrict__ zero, long long zero_count, IdentityShare id) {
     lp_grid_release();
     lp_grid_wait();
     clear_on_the_side(zero, zero_count);
     const long long t = blockIdx.y;
+    if (id.x) add_identity_share(id, weights, ldw, t, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x);
     const int octets = E * ff / 8;
     for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < octets; o += gridDim.x * blockDim.x) {
         const int c = o * 8;
@@ -326,9 +349,18 @@ extern "C" int lp_route(const float* z, int ldz, float* weights, int ldw, int T,
 
 // zero (optional): a float32 buffer of zero_count values cleared on the side, for the product after the scaling when it
 // sums partial results into its output.
+// id_x (optional): float32 [T, d], to which h [T, d] (dtype code id_dtype) times the sum of the weights' columns
+// id_first .. id_first + id_count - 1 is added in the same launch (experts that pass their input on).
 extern "C" int lp_expert_scale(void* hidden, int dtype, int ldh, const float* weights, int ldw, int T, int E, int ff,
-                               float* zero, long long zero_count, cudaStream_t stream) {
+                               float* zero, long long zero_count, float* id_x, const void* id_h, int id_dtype, int id_first,
+                               int id_count, int id_d, cudaStream_t stream) {
     if (T <= 0 || E <= 0 || ff <= 0) return 0;
+    IdentityShare id{};
+    if (id_x && id_count > 0) {
+        if (!id_h || id_d <= 0 || id_first < 0 || id_first + id_count > ldw || (id_dtype != LP_F32 && id_dtype != LP_BF16))
+            LP_REFUSE("expert_scale: identity columns %d..%d of rows of %d, width %d, dtype code %d", id_first, id_first + id_count - 1, ldw, id_d, id_dtype);
+        id = IdentityShare{id_x, id_h, id_dtype == LP_BF16 ? 1 : 0, id_first, id_count, id_d};
+    }
     if (ldh < E * ff || ldw < E) LP_REFUSE("expert_scale: rows of %d and %d values for %d experts of %d", ldh, ldw, E, ff);
     const long long n = (long long)T * E * ff;
     long long blocks = (n + 255) / 256;
@@ -337,11 +369,11 @@ extern "C" int lp_expert_scale(void* hidden, int dtype, int ldh, const float* we
         const int octets = E * ff / 8;
         int bx = (octets + 255) / 256;
         if (bx > 64) bx = 64;
-        lp_launch(expert_scale_vec8_kernel, dim3(bx, T), 256, 0, stream, (__nv_bfloat16*)hidden, ldh, weights, ldw, E, ff, zero, zero_count);
+        lp_launch(expert_scale_vec8_kernel, dim3(bx, T), 256, 0, stream, (__nv_bfloat16*)hidden, ldh, weights, ldw, E, ff, zero, zero_count, id);
         return lp_check_launch("expert_scale");
     }
-    if (dtype == LP_F32) lp_launch(expert_scale_kernel<float>, (unsigned)blocks, 256, 0, stream, (float*)hidden, ldh, weights, ldw, T, E, ff, zero, zero_count);
-    else if (dtype == LP_BF16) lp_launch(expert_scale_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, (__nv_bfloat16*)hidden, ldh, weights, ldw, T, E, ff, zero, zero_count);
+    if (dtype == LP_F32) lp_launch(expert_scale_kernel<float>, (unsigned)blocks, 256, 0, stream, (float*)hidden, ldh, weights, ldw, T, E, ff, zero, zero_count, id);
+    else if (dtype == LP_BF16) lp_launch(expert_scale_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, (__nv_bfloat16*)hidden, ldh, weights, ldw, T, E, ff, zero, zero_count, id);
     else LP_REFUSE("expert_scale: dtype code %d", dtype);
     return lp_check_launch("expert_scale");
 }

@@ -42,7 +42,7 @@ _SIGNATURES = {
     },
     "routing": {
         "lp_route": [_P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
-        "lp_expert_scale": [_P, _I, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P],
+        "lp_expert_scale": [_P, _I, _I, _P, _I, _I, _I, _I, _P, ctypes.c_longlong, _P, _P, _I, _I, _I, _I, _P],
         "lp_route_top": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
         "lp_expert_act": [_P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _F, _F, _P, ctypes.c_longlong, _P],
         "lp_route_softmax": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P],
@@ -1804,18 +1804,29 @@ def identity_experts(x: torch.Tensor, h: torch.Tensor, weights: torch.Tensor, fi
 
 
 def expert_scale(hidden: torch.Tensor, weights: torch.Tensor, expert_size: int, clear: Optional[torch.Tensor] = None,
-                 num_experts: Optional[int] = None) -> torch.Tensor:
+                 num_experts: Optional[int] = None, identity=None) -> torch.Tensor:
     """hidden[t, e * expert_size + j] *= weights[t, e] in place for the E experts of ``weights`` [T, E] (``num_experts``:
-    for its first so many columns only); columns of ``hidden`` beyond E * expert_size are left as they are."""
+    for its first so many columns only); columns of ``hidden`` beyond E * expert_size are left as they are.
+    ``identity`` = (x, h, first, count): in the same launch x[t] += h[t] * sum(weights[t, first:first + count]), as
+    :func:`identity_experts` does (x float32 [T, d], h [T, d])."""
     _want(hidden, "expert_scale hidden", ndim=2)
     _want(weights, "expert_scale weights", torch.float32, 2)
     T, ldw = weights.shape
     E = ldw if num_experts is None else int(num_experts)
     if hidden.shape[0] != T or hidden.shape[1] < E * expert_size or not 0 < E <= ldw:
         raise KernelError(f"expert_scale: hidden {tuple(hidden.shape)} for {E} experts of {expert_size}")
+    id_args = (None, None, 0, 0, 0, 0)
+    if identity is not None:
+        x, h, first, count = identity
+        _want(x, "expert_scale identity x", torch.float32, 2)
+        _want(h, "expert_scale identity h", ndim=2)
+        if h.shape != x.shape or x.shape[0] != T or first < 0 or first + count > ldw:
+            raise KernelError(f"expert_scale: identity x {tuple(x.shape)}, h {tuple(h.shape)}, columns {first}..{first + count - 1} of {ldw}")
+        id_args = (x.data_ptr(), h.data_ptr(), _code(h, "expert_scale identity h"), int(first), int(count), x.shape[1])
     lib = library("routing")
     _check(lib, lib.lp_expert_scale(hidden.data_ptr(), _code(hidden, "expert_scale hidden"), hidden.shape[1],
-                                    weights.data_ptr(), ldw, T, E, int(expert_size), *_clear_args(clear, "expert_scale"), _stream()))
+                                    weights.data_ptr(), ldw, T, E, int(expert_size), *_clear_args(clear, "expert_scale"),
+                                    *id_args, _stream()))
     return hidden
 
 

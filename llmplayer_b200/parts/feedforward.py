@@ -372,6 +372,7 @@ class Mixture(Part):
                 ops.route(logits, weights, groups=r.groups, keep=r.keep_groups, top=r.top)
         h = ctx.buffer("ffn_hidden", (T, self.total), self.runtime.act_dtype)
         clear = residual if overwrite and residual.dtype == torch.float32 and self.down.needs_zero(T) else None
+        rides = False
         if s.activation == "clamped":
             z = ctx.buffer("ffn_up", (T, 2 * self.total), torch.float32)
             with ops.section("ffn.gate_up"):
@@ -382,8 +383,12 @@ class Mixture(Part):
         else:
             with ops.section("ffn.gate_up"):
                 self.gate_up.swiglu(x, h, ctx)
+            # experts that are the identity (the feed-forward's input itself, times the token's weights for them) ride
+            # along in the same launch when the experts' outputs are added to the stream afterwards
+            rides = r.identity_experts > 0 and not overwrite and residual.dtype == torch.float32
             with ops.section("ffn.weights"):
-                ops.expert_scale(h, weights, s.expert_size, clear=clear, num_experts=r.num_experts)
+                ops.expert_scale(h, weights, s.expert_size, clear=clear, num_experts=r.num_experts,
+                                 identity=(residual, x, r.num_experts, r.identity_experts) if rides else None)
         with ops.section("ffn.down"):
             if clear is not None:
                 ctx.note_cleared()
@@ -391,8 +396,8 @@ class Mixture(Part):
                 self.down.store(h, residual, ctx)
             else:
                 self.down.accumulate(h, residual, ctx)
-        if r.identity_experts:
-            # experts that are the identity: the feed-forward's input itself, times the token's weights for them
+        if r.identity_experts and not rides:
+            # (a step that stores the experts' outputs adds the identities' share behind them)
             with ops.section("ffn.identity"):
                 ops.identity_experts(residual, x, weights, r.num_experts, r.identity_experts)
         return False

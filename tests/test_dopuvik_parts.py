@@ -80,6 +80,14 @@ def test_identity_experts_pass_their_input_on():
     ref = hidden.double().cpu() * w[:, :4].double().cpu().repeat_interleave(8, dim=1)
     ops.expert_scale(hidden, w, 8, num_experts=4)
     assert rel(hidden, ref) < 2e-6
+    # both in one launch: the identities' share rides with the scaling (generic kernel and the eight-column one)
+    for dtype, ff, lim in ((torch.float32, 5, 2e-6), (torch.bfloat16, 8, 4e-3)):
+        hidden = torch.randn(T, 4 * ff).to(dtype).cuda()
+        want_hidden = hidden.double().cpu() * w[:, :4].double().cpu().repeat_interleave(ff, dim=1)
+        got = x.clone()
+        ops.expert_scale(hidden, w, ff, num_experts=4, identity=(got, h.to(dtype).cuda(), 4, 3))
+        want_x = x.double().cpu() + h.to(dtype).double() * w[:, 4:].double().cpu().sum(-1, keepdim=True)
+        assert rel(hidden, want_hidden) < (2e-6 if dtype == torch.float32 else 4e-3) and rel(got, want_x) < 2e-6
 
 
 # --------------------------------------------------------------------------- short convolution
