@@ -290,7 +290,14 @@ delta_combine_kernel(float* __restrict__ state, const int* __restrict__ slots, c
             float acc = blockp[(long long)j * dk + c];                    // L_p[c][j]
             const float* P = blockp + (long long)dv * dk + c;             // P_p[c][m] lies at column dv + m, channel c
             int m = 0;
-            for (; m + 8 <= dk; m += 8) {                                 // eight loads in flight: a block has few warps
+            for (; m + 32 <= dk; m += 32) {                               // 32 loads in flight: a block has few warps, and
+                float pv[32];                                             // every chunk waits for the one before it
+#pragma unroll
+                for (int u = 0; u < 32; ++u) pv[u] = __ldcg(P + (long long)(m + u) * dk);
+#pragma unroll
+                for (int u = 0; u < 32; ++u) acc = fmaf(pv[u], col[m + u], acc);
+            }
+            for (; m + 8 <= dk; m += 8) {
                 float pv[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) pv[u] = __ldcg(P + (long long)(m + u) * dk);

@@ -1388,6 +1388,8 @@ def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torc
         raise KernelError(f"gla_scan: {H} heads over {qk_heads} query / key heads")
     chunks, chunk_state, chunk_decay = 1, None, None
     # the delta rule's passes are bound by their chain of tokens, not by arithmetic: shorter chunks, more of them
+    # (measured at 4 heads of 64 x 64 over 2,048 tokens: chunks of 128 / 64 / 32: 0.28 / 0.22 / 0.34 ms; the chunks'
+    # combination, a chain over the chunks, costs about 5 us per chunk)
     chunk = GLA_CHUNK // 2 if delta_strength is not None else GLA_CHUNK
     if scratch is not None and max_new >= GLA_CHUNKED_FROM and B * -(-max_new // chunk) <= 65535:
         chunks = -(-max_new // chunk)
