@@ -1,8 +1,9 @@
 """The cache of a model: per-sequence slots, paged keys and values in groups of
 layers with equal needs, and a per-sequence state area of fixed size.
 
-What a run of a layer needs is said by its mixer (a :class:`KVRequest`, a
-:class:`StateRequest`, a tuple of those for several blocks, or nothing). Runs with the same key/value geometry and
+What a run of a layer needs is said by its mixer (a :class:`KVRequest`, a :class:`RowsRequest`, a
+:class:`StateRequest`, a tuple of those for several blocks, a :class:`BundleRequest` of such requests for a
+mixer made of several mixers, or nothing). Runs with the same key/value geometry and
 window share one :class:`KVGroup` — one storage tensor and one page map —
 so layers that keep all keys and layers that keep a window of them have storage
 of their own. State requests get one row per slot each, zeroed when the slot is
@@ -112,7 +113,7 @@ class StateView:
 class SequenceCache:
     def __init__(self, requests: Sequence[object], *, max_tokens: int, max_slots: Optional[int], kv_dtype: torch.dtype,
                  device):
-        """``requests[i]``: what run i of the schedule keeps (KVRequest, StateRequest or None)."""
+        """``requests[i]``: what run i of the schedule keeps (a paged request, state requests, a bundle of those, or None)."""
         if max_tokens <= 0:
             raise CacheError(f"max_tokens must be positive, got {max_tokens}")
         self.device = device

@@ -52,9 +52,9 @@ class MixerPair(Part):
         ask = getattr(self.left, "buffer_to_clear", None)
         return ask(ctx, tokens) if ask is not None else None
 
-    def _run(self, member, args, ctx, view, x, name: str, prefix: str):
+    def _run(self, member, args, ctx, view, x, width: int, name: str, prefix: str):
         """Run a member into a float32 buffer of its own; returns (buffer, the vector it left to the caller or None)."""
-        y = ctx.buffer(name, (x.shape[0], self._width), torch.float32)
+        y = ctx.buffer(name, (x.shape[0], width), torch.float32)
         kwargs = {}
         if "overwrite" in args:
             kwargs["overwrite"] = True
@@ -71,12 +71,12 @@ class MixerPair(Part):
         """Adds the pair's result into ``residual`` (``overwrite``: the stream is set to zero first)."""
         if isinstance(x, PendingNorm):
             x = x.tensor()
-        self._width = residual.shape[1]
+        width = residual.shape[1]
         views = cache.members if cache is not None else (None, None)
         if overwrite:
             residual.zero_()
-        a, a_vec = self._run(self.left, self._args[0], ctx, views[0], x, "pair_left", "left.")
-        b, b_vec = self._run(self.right, self._args[1], ctx, views[1], x, "pair_right", "right.")
+        a, a_vec = self._run(self.left, self._args[0], ctx, views[0], x, width, "pair_left", "left.")
+        b, b_vec = self._run(self.right, self._args[1], ctx, views[1], x, width, "pair_right", "right.")
         with ops.section("mixer.sum"):
             ops.scaled_sum(residual, a, self.spec.left_scale, b, self.spec.right_scale, a_vector=a_vec, b_vector=b_vec)
         return False
